@@ -9,6 +9,12 @@ to be written into them and come back when the request ends, is pre-empted, or -
 group - when every later query is past them.  The block table keeps -1 where a page was
 given back.  Every request also holds one state slot; mixers with `StateNeed` get a tensor
 [max_seqs, *shape] that is zeroed when the slot is handed to a new request.
+
+A group whose values are not as wide as its keys (`KvCacheNeed.value_dim`) keeps its pages flat:
+[cache slots, num_pages, kv_heads * page_size * (head_dim + value_dim)], a page's key rows first, then its
+value rows.  A chunk group (`KvCacheNeed.chunk`) gives a page back once the block of positions that the next
+query lies in starts above it.  A cache slot whose mixer is made of several mixers (`CompositeNeed`) has one
+sub-view per member, each handled as a cache slot of its own.
 """
 from __future__ import annotations
 
@@ -18,7 +24,7 @@ from typing import Dict, Hashable, List, Optional, Tuple
 import torch
 
 from ..errors import KvExhausted, SchedulerError
-from ..parts.base import KvCacheNeed, StateNeed
+from ..parts.base import CompositeNeed, KvCacheNeed, StateNeed
 from .pools import PagePool, SlotPool
 
 
@@ -26,8 +32,9 @@ from .pools import PagePool, SlotPool
 class CacheView:
     """What a mixer sees of its cache slot."""
     group: Optional[int]                 # index of the page group (None: no pages)
-    kv: Optional[torch.Tensor]           # [num_pages, planes, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor]           # [num_pages, planes, kv_heads, page_size, head_dim] (flat pages: [num_pages, elements])
     state: Optional[torch.Tensor] = None  # [max_seqs, *shape]
+    parts: Tuple["CacheView", ...] = ()   # one view per member of a mixer made of several mixers
 
 
 @dataclass
@@ -46,18 +53,31 @@ class _Request:
     first_live: List[int] = field(default_factory=list)     # per group: first logical block still held
 
 
+def flat_needs(needs: Dict[int, object]) -> Dict[object, object]:
+    """cache slot -> need, with the members of a `CompositeNeed` under the keys (slot, member index)."""
+    out: Dict[object, object] = {}
+    for slot in sorted(needs):
+        need = needs[slot]
+        if isinstance(need, CompositeNeed):
+            for i, member in enumerate(need.parts):
+                out[(slot, i)] = member
+        else:
+            out[slot] = need
+    return out
+
+
 class CacheManager:
     def __init__(self, needs: Dict[int, object], num_pages: int, page_size: int, max_seqs: int,
                  dtype: torch.dtype = torch.float32, device="cpu", allocate: bool = True):
         self.page_size, self.num_pages, self.max_seqs = page_size, num_pages, max_seqs
         self.dtype, self.device = dtype, device
         self.groups: List[_Group] = []
-        self._slot_group: Dict[int, int] = {}
-        self._slot_index: Dict[int, int] = {}
-        self._state: Dict[int, torch.Tensor] = {}
-        self._state_needs: Dict[int, StateNeed] = {}
-        for slot in sorted(needs):
-            need = needs[slot]
+        self._slot_group: Dict[object, int] = {}
+        self._slot_index: Dict[object, int] = {}
+        self._state: Dict[object, torch.Tensor] = {}
+        self._state_needs: Dict[object, StateNeed] = {}
+        self._members = {slot: len(need.parts) for slot, need in needs.items() if isinstance(need, CompositeNeed)}
+        for slot, need in flat_needs(needs).items():
             if isinstance(need, KvCacheNeed):
                 for gi, g in enumerate(self.groups):
                     if g.need == need:
@@ -73,12 +93,15 @@ class CacheManager:
             elif need is not None:
                 raise SchedulerError(f"cache slot {slot}: unknown kind of need {need!r}")
         self.slots = SlotPool(max_seqs)
-        self._has_window = any(g.need.window is not None for g in self.groups)
+        self._has_window = any(g.need.window is not None or g.need.chunk is not None for g in self.groups)
         self.requests: Dict[Hashable, _Request] = {}
         if allocate:
             for g in self.groups:
-                g.tensor = torch.zeros((len(g.cache_slots), num_pages, g.need.planes, g.need.num_kv_heads, page_size,
-                                        g.need.head_dim), dtype=dtype, device=device)
+                if g.need.flat_pages:
+                    shape = (len(g.cache_slots), num_pages, g.need.num_kv_heads * page_size * g.need.row_elements)
+                else:
+                    shape = (len(g.cache_slots), num_pages, g.need.planes, g.need.num_kv_heads, page_size, g.need.head_dim)
+                g.tensor = torch.zeros(shape, dtype=dtype, device=device)
             for slot, need in self._state_needs.items():
                 self._state[slot] = torch.zeros((max_seqs, *need.shape), dtype=getattr(torch, need.dtype), device=device)
 
@@ -87,13 +110,13 @@ class CacheManager:
     def bytes_per_page(needs: Dict[int, object], page_size: int, dtype: torch.dtype) -> int:
         """Bytes that one more page per group costs over all cache slots."""
         el = torch.empty((), dtype=dtype).element_size()
-        return sum(n.planes * n.num_kv_heads * page_size * n.head_dim * el for n in needs.values() if isinstance(n, KvCacheNeed))
+        return sum(n.num_kv_heads * page_size * n.row_elements * el for n in flat_needs(needs).values() if isinstance(n, KvCacheNeed))
 
     @staticmethod
     def state_bytes_per_request(needs: Dict[int, object]) -> int:
         """Bytes of fixed-size state that one request slot holds over all cache slots."""
         total = 0
-        for n in needs.values():
+        for n in flat_needs(needs).values():
             if isinstance(n, StateNeed):
                 count = 1
                 for d in n.shape:
@@ -101,7 +124,9 @@ class CacheManager:
                 total += count * torch.empty((), dtype=getattr(torch, n.dtype)).element_size()
         return total
 
-    def view(self, cache_slot: int) -> CacheView:
+    def view(self, cache_slot) -> CacheView:
+        if cache_slot in self._members:
+            return CacheView(None, None, None, tuple(self.view((cache_slot, i)) for i in range(self._members[cache_slot])))
         gi = self._slot_group.get(cache_slot)
         kv = None
         if gi is not None and self.groups[gi].tensor is not None:
@@ -119,7 +144,7 @@ class CacheManager:
         out = []
         for g in self.groups:
             full = self.blocks_for(num_tokens)
-            w = g.need.window
+            w = g.need.window if g.need.window is not None else g.need.chunk
             if w is None:
                 out.append(full)
             else:
@@ -191,17 +216,22 @@ class CacheManager:
         return out
 
     def release_passed(self, req: Hashable) -> int:
-        """Give back the pages of window groups that no later query can see.  The next query
-        sits at position >= num_tokens and sees keys > position - window."""
+        """Give back the pages of window and chunk groups that no later query can see.  The next query
+        sits at position >= num_tokens and sees keys > position - window, and - in a chunk group - no key
+        below the start of its own block of `chunk` positions."""
         r = self.requests[req]
         freed = 0
         if not self._has_window:
             return 0
         for gi, g in enumerate(self.groups):
-            w = g.need.window
-            if w is None:
+            w, c = g.need.window, g.need.chunk
+            if w is None and c is None:
                 continue
-            first_needed = max(0, r.num_tokens - w + 1)          # lowest key position still visible
+            first_needed = 0                                     # lowest key position still visible
+            if w is not None:
+                first_needed = max(0, r.num_tokens - w + 1)
+            if c is not None:
+                first_needed = max(first_needed, (r.num_tokens // c) * c)
             first_block = first_needed // self.page_size
             table = r.tables[gi]
             give = []

@@ -2,6 +2,7 @@ from .spec import PartSpec, LayerSpec, RunEntry, ModelSpec, default_run_order, m
 from .model_config import DenseDecoderConfig, LlamaConfig, Qwen2Config, RopeScaling, read_config_json
 from .tufirax_config import TufiraxConfig, TufiraxLayer
 from .vipelix_config import VipelixConfig, VipelixLayer
+from .tibepel_config import TibepelConfig, TibepelLayer
 from .registry import (register_architecture, unregister_architecture, known_architectures,
                        config_from_dict, load_config)
 from .engine_config import EngineConfig, canonical_dtype

@@ -12,6 +12,7 @@ from ..errors import ConfigError
 from .model_config import LlamaConfig, Qwen2Config, read_config_json
 from .tufirax_config import TufiraxConfig
 from .vipelix_config import VipelixConfig
+from .tibepel_config import TibepelConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
 
@@ -55,3 +56,4 @@ register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Qwen2ForCausalLM", Qwen2Config)
 register_architecture("Tufirax", TufiraxConfig)
 register_architecture("Vipelix", VipelixConfig)
+register_architecture("Tibepel", TibepelConfig)

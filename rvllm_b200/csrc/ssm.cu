@@ -532,3 +532,99 @@ RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void
                              N, groups, seg_tokens, max_segs);
     return rv_launch_status();
 }
+
+// ------------------------------------------------------------------ the recurrence with one state row per channel
+// The older form of the selective scan: every channel c has its own decays A[c, :] and its own step size,
+//     S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n ,   y_c = sum_n S[c, n] C_n + D_c u_c ,   out_c = y_c silu(z_c)
+// with dt_c = softplus(raw_c + bias_c); B and C are shared by all channels of a token.  S lives as [inner][N] at
+// offset 0 of the request's state row.  A channel is served by `parts` neighbouring lanes with up to SCAN1_NS states
+// each (partial sums meet by shuffles), a block by 128 threads; grid (channel blocks, sequences).  The tokens' B
+// and C wait in shared memory in chunks of SCAN1_CHUNK tokens.
+#define SCAN1_NS 16
+#define SCAN1_CHUNK 16
+
+__global__ void __launch_bounds__(128)
+selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
+                       const float* __restrict__ A, const float* __restrict__ bc, int bc_stride, int b_col0, int c_col0,
+                       const float* __restrict__ d_skip, const void* __restrict__ z, int z_dtype, int z_stride, int z_col0,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, float* __restrict__ state,
+                       size_t state_stride, void* __restrict__ out, int out_dtype, int inner, int N, int parts) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ float sBC[];                     // [SCAN1_CHUNK][2 N]
+    const int seq = blockIdx.y;
+    const int slot = state_slots[seq];
+    if (slot < 0) return;
+    const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
+    const int per_block = blockDim.x / parts;
+    const int c = blockIdx.x * per_block + threadIdx.x / parts;
+    const int part = threadIdx.x % parts;
+    const bool live = c < inner;
+    const int n0 = part * SCAN1_NS;
+    float S[SCAN1_NS], a[SCAN1_NS];
+    float* srow = state + (size_t)slot * state_stride + (size_t)c * N;
+#pragma unroll
+    for (int i = 0; i < SCAN1_NS; ++i) {
+        const bool ok = live && n0 + i < N;
+        S[i] = ok ? srow[n0 + i] : 0.f;
+        a[i] = ok ? A[(size_t)c * N + n0 + i] : 0.f;
+    }
+    const float bias = live ? dt_bias[c] : 0.f, dsk = live ? d_skip[c] : 0.f;
+    for (int t0 = 0; t0 < n_tok; t0 += SCAN1_CHUNK) {
+        const int nt = min(SCAN1_CHUNK, n_tok - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * 2 * N; i += blockDim.x) {
+            const int tt = i / (2 * N), j = i - tt * 2 * N;
+            sBC[i] = bc[(size_t)(start + t0 + tt) * bc_stride + (j < N ? b_col0 + j : c_col0 + j - N)];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {                   // (threads beyond the last channel walk along: the shuffles need every lane)
+            const size_t row = (size_t)(start + t0 + tt);
+            const float raw = (live ? dt_raw[row * inner + c] : 0.f) + bias;
+            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
+            const float uv = live ? rv_load_any(u, u_dtype, row * inner + c) : 0.f;
+            const float du = dt * uv;
+            const float* B = sBC + tt * 2 * N + n0;
+            const float* C = B + N;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < SCAN1_NS; ++i) {
+                if (n0 + i < N) {
+                    S[i] = fmaf(expf(dt * a[i]), S[i], du * B[i]);
+                    acc = fmaf(S[i], C[i], acc);
+                }
+            }
+            for (int o = 1; o < parts; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (part == 0 && live) {
+                const float y = fmaf(dsk, uv, acc);
+                const float zv = rv_load_any(z, z_dtype, row * z_stride + z_col0 + c);
+                rv_store_any(out, out_dtype, row * inner + c, y * (zv / (1.0f + expf(-zv))));
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < SCAN1_NS; ++i)
+            if (n0 + i < N) srow[n0 + i] = S[i];
+    }
+}
+
+RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw, const float* dt_bias, const float* A,
+                                 const float* bc, int bc_stride, int b_col0, int c_col0, const float* d_skip, const void* z,
+                                 int z_dtype, int z_stride, int z_col0, const int* cu_seqlens, const int* state_slots, float* state,
+                                 long long state_stride, void* out, int out_dtype, int n_seqs, int inner, int N, cudaStream_t stream) {
+    if (n_seqs < 0 || inner <= 0 || N <= 0 || N > 32 * SCAN1_NS || n_seqs > 65535) return RV_ERR_BAD_SIZE;
+    if (b_col0 < 0 || c_col0 < 0 || b_col0 + N > bc_stride || c_col0 + N > bc_stride || z_col0 < 0 || z_col0 + inner > z_stride ||
+        state_stride < (long long)inner * N)
+        return RV_ERR_BAD_SIZE;
+    if ((u_dtype | z_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (n_seqs == 0) return RV_OK;
+    int parts = 1;
+    while (parts * SCAN1_NS < N) parts <<= 1;          // a power of two of at most 32 lanes of one warp
+    const int per_block = 128 / parts;
+    RV_LAUNCH_ST = rv_launch(selective_scan1_kernel, dim3((inner + per_block - 1) / per_block, n_seqs), dim3(128),
+                             (size_t)SCAN1_CHUNK * 2 * N * sizeof(float), stream, u, u_dtype, dt_raw, dt_bias, A, bc, bc_stride,
+                             b_col0, c_col0, d_skip, z, z_dtype, z_stride, z_col0, cu_seqlens, state_slots, state,
+                             (size_t)state_stride, out, out_dtype, inner, N, parts);
+    return rv_launch_status();
+}

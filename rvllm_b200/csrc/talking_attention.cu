@@ -1,0 +1,272 @@
+// Attention whose softmax weights are mixed across the heads ("talking heads"), over the paged cache; keys and
+// values may differ in width, a distance bias may be taken off the scores, and a query may be limited to the keys
+// of its own block of `chunk` positions.
+//
+//   kv_prepare          rows [q | k | v] of the stacked product -> q in the activations' type, k and v into the
+//                       token's cache slot; v is first divided by its root mean square per head (option)
+//   talking_attention   s_h(i, j) = scale q_h(i) . k(j) - r1_h ln(1 + r2_h (i - j));  p_h = softmax_j s_h over the
+//                       visible keys;  p'_h = sum_g talk[h, g] p_g;  o_h(i) = sum_j p'_h(i, j) v_{kv(h)}(j)
+//
+// A page of the cache holds the key rows of all its kv heads, [nkv][page_size][hd], and behind them the value rows,
+// [nkv][page_size][vd] (with hd = vd this is the layout [2][nkv][page_size][hd] of the other attention kernels).
+//
+// The weights of ALL heads of a token have to be final before they can be mixed, so a token is one CTA's work:
+// a first walk over the visible keys finds every head's maximum and denominator, a second one forms a tile of
+// normalised weights for all heads in shared memory, mixes them with `talk`, and adds the tile's values to the
+// outputs (which wait in shared memory).  Scores, weights, the bias and the mixing are float32 whatever the cache
+// holds.  The q_len tokens a sequence brings to a step are the tail of its ctx_len cached tokens; ctx_len <= 0
+// marks a padded row (zeros are written, no table is read).
+#include "common.cuh"
+
+#define TA_THREADS 256
+#define TA_WARPS 8
+#define TA_TILE 32
+
+__device__ __forceinline__ float ta_load(const void* p, int dtype, size_t i) {
+    return dtype == RV_DTYPE_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ __forceinline__ void ta_store(void* p, int dtype, size_t i, float v) {
+    if (dtype == RV_DTYPE_F32) ((float*)p)[i] = v;
+    else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+// ------------------------------------------------------------------ q, and k | v into the cache
+// One CTA of 128 threads per token.
+template <typename TC>
+__global__ void __launch_bounds__(128)
+kv_prepare_kernel(const void* __restrict__ proj, int p_dtype, int p_stride, const int* __restrict__ slot_mapping,
+                  TC* __restrict__ cache, void* __restrict__ q_out, int q_dtype, int nh, int nkv, int hd, int vd, int page_size,
+                  float eps, int norm_v, int write_kv) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const int t = blockIdx.x;
+    const size_t row = (size_t)t * p_stride;
+    const int qw = nh * hd, kw = nkv * hd;
+    for (int i = threadIdx.x; i < qw; i += blockDim.x) ta_store(q_out, q_dtype, (size_t)t * qw + i, ta_load(proj, p_dtype, row + i));
+    if (!write_kv) return;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const size_t page_elems = (size_t)nkv * page_size * (hd + vd);
+    TC* page = cache + (size_t)(slot / page_size) * page_elems;
+    const int off = slot % page_size;
+    for (int i = threadIdx.x; i < kw; i += blockDim.x) {
+        const int g = i / hd, e = i - g * hd;
+        page[((size_t)g * page_size + off) * hd + e] = rv_from_float<TC>(ta_load(proj, p_dtype, row + qw + i));
+    }
+    TC* vpage = page + (size_t)nkv * page_size * hd;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int g = warp; g < nkv; g += nwarps) {
+        const size_t vb = row + qw + kw + (size_t)g * vd;
+        float r = 1.0f;
+        if (norm_v) {
+            float ss = 0.f;
+            for (int e = lane; e < vd; e += 32) {
+                const float v = ta_load(proj, p_dtype, vb + e);
+                ss = fmaf(v, v, ss);
+            }
+            ss = rv_warp_sum(ss);
+            r = 1.0f / sqrtf(ss / (float)vd + eps);
+        }
+        for (int e = lane; e < vd; e += 32)
+            vpage[((size_t)g * page_size + off) * vd + e] = rv_from_float<TC>(ta_load(proj, p_dtype, vb + e) * r);
+    }
+}
+
+RV_EXPORT int rv_kv_prepare(const void* proj, int p_dtype, int p_stride, const int* slot_mapping, void* cache, int cache_dtype,
+                            void* q_out, int q_dtype, int n_tokens, int nh, int nkv, int hd, int vd, int page_size, float eps,
+                            int norm_v, int write_kv, cudaStream_t stream) {
+    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || vd <= 0 || page_size <= 0 || p_stride < nh * hd + nkv * (hd + vd))
+        return RV_ERR_BAD_SIZE;
+    if ((p_dtype | q_dtype | cache_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (n_tokens == 0) return RV_OK;
+    if (cache_dtype == RV_DTYPE_F32)
+        RV_LAUNCH_ST = rv_launch(kv_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, proj, p_dtype, p_stride, slot_mapping,
+                                 (float*)cache, q_out, q_dtype, nh, nkv, hd, vd, page_size, eps, norm_v, write_kv);
+    else
+        RV_LAUNCH_ST = rv_launch(kv_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, proj, p_dtype, p_stride,
+                                 slot_mapping, (__nv_bfloat16*)cache, q_out, q_dtype, nh, nkv, hd, vd, page_size, eps, norm_v, write_kv);
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ the attention itself
+// q . k over hd elements; q waits in shared memory as float.  VEC: 16-byte reads of the key row.
+template <typename T, bool VEC>
+__device__ __forceinline__ float ta_dot(const T* __restrict__ kp, const float* __restrict__ qs, int hd) {
+    float s = 0.f;
+    if constexpr (VEC && sizeof(T) == 2) {
+        for (int e = 0; e < hd; e += 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(kp + e);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float4 qa = *reinterpret_cast<const float4*>(qs + e), qb = *reinterpret_cast<const float4*>(qs + e + 4);
+            const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+            const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+            s = fmaf(f0.x, qa.x, s); s = fmaf(f0.y, qa.y, s); s = fmaf(f1.x, qa.z, s); s = fmaf(f1.y, qa.w, s);
+            s = fmaf(f2.x, qb.x, s); s = fmaf(f2.y, qb.y, s); s = fmaf(f3.x, qb.z, s); s = fmaf(f3.y, qb.w, s);
+        }
+    } else if constexpr (VEC) {
+        for (int e = 0; e < hd; e += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kp + e);
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + e);
+            s = fmaf(k4.x, q4.x, s); s = fmaf(k4.y, q4.y, s); s = fmaf(k4.z, q4.z, s); s = fmaf(k4.w, q4.w, s);
+        }
+    } else {
+        for (int e = 0; e < hd; ++e) s = fmaf(rv_to_float(kp[e]), qs[e], s);
+    }
+    return s;
+}
+
+// The score of head h against the key at position j (one lane's work).
+template <typename T, bool VEC>
+__device__ __forceinline__ float ta_score(const T* __restrict__ cache, const int* __restrict__ table, size_t page_elems, int page_size,
+                                          int hd, int kvh, int j, int pos, const float* __restrict__ qs, float scale, float r1, float r2,
+                                          bool biased) {
+    const int page = table[j / page_size];
+    const T* kp = cache + (size_t)page * page_elems + ((size_t)kvh * page_size + (j % page_size)) * hd;
+    float s = ta_dot<T, VEC>(kp, qs, hd) * scale;
+    if (biased) s -= r1 * log1pf(r2 * (float)(pos - j));
+    return s;
+}
+
+// Shared memory (floats): q [nh * hd] | O [nh * vd] | P [nh][TA_TILE] | P' [nh][TA_TILE] | talk [nh * nh] | m [nh] | 1/l [nh],
+// and TA_TILE 64-bit offsets of the tile's value rows.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(TA_THREADS)
+talking_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_tables,
+                         const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ token_seq,
+                         T* __restrict__ out, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, float scale,
+                         const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ talk, int chunk) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ __align__(16) unsigned char ta_smem[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t = blockIdx.x;
+    const int seq = token_seq[t];
+    const int ctx = seq >= 0 ? ctx_lens[seq] : 0;
+    T* o = out + (size_t)t * nh * vd;
+    if (ctx <= 0) {
+        for (int i = tid; i < nh * vd; i += TA_THREADS) o[i] = rv_from_float<T>(0.f);
+        return;
+    }
+    size_t* vrow = reinterpret_cast<size_t*>(ta_smem);
+    float* qs = reinterpret_cast<float*>(ta_smem + TA_TILE * sizeof(size_t));
+    float* Os = qs + (size_t)nh * hd;
+    float* P = Os + (size_t)nh * vd;
+    float* PM = talk ? P + nh * TA_TILE : P;
+    float* talk_s = P + 2 * nh * TA_TILE;
+    float* ms = talk_s + nh * nh;
+    float* linv = ms + nh;
+
+    const int q_start = cu_seqlens[seq];
+    const int q_len = cu_seqlens[seq + 1] - q_start;
+    const int pos = ctx - q_len + (t - q_start);
+    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    const int rep = nh / nkv;
+    const int* table = block_tables + (size_t)seq * max_blocks;
+    const size_t page_elems = (size_t)nkv * page_size * (hd + vd);
+    const size_t v_off = (size_t)nkv * page_size * hd;
+    const bool biased = r1 != nullptr;
+
+    for (int i = tid; i < nh * hd; i += TA_THREADS) qs[i] = rv_to_float(q[(size_t)t * nh * hd + i]);
+    for (int i = tid; i < nh * vd; i += TA_THREADS) Os[i] = 0.f;
+    if (talk)
+        for (int i = tid; i < nh * nh; i += TA_THREADS) talk_s[i] = talk[i];
+    __syncthreads();
+
+    // every head's maximum and denominator: a warp per head, a lane per key, joined at the end
+    for (int h = warp; h < nh; h += TA_WARPS) {
+        const float a1 = biased ? r1[h] : 0.f, a2 = biased ? r2[h] : 0.f;
+        float m = -INFINITY, l = 0.f;
+        for (int j = lo + lane; j <= pos; j += 32) {
+            const float s = ta_score<T, VEC>(cache, table, page_elems, page_size, hd, h / rep, j, pos, qs + (size_t)h * hd, scale, a1, a2, biased);
+            const float m_new = fmaxf(m, s);
+            l = l * expf(m - m_new) + expf(s - m_new);
+            m = m_new;
+        }
+        const float M = rv_warp_max(m);
+        l = rv_warp_sum(m == -INFINITY ? 0.f : l * expf(m - M));
+        if (lane == 0) {
+            ms[h] = M;
+            linv[h] = 1.0f / l;
+        }
+    }
+    __syncthreads();
+
+    for (int j0 = lo; j0 <= pos; j0 += TA_TILE) {
+        const int nk = min(TA_TILE, pos - j0 + 1);
+        // the tile's normalised weights, head by head
+        for (int h = warp; h < nh; h += TA_WARPS) {
+            float p = 0.f;
+            if (lane < nk) {
+                const float a1 = biased ? r1[h] : 0.f, a2 = biased ? r2[h] : 0.f;
+                const float s = ta_score<T, VEC>(cache, table, page_elems, page_size, hd, h / rep, j0 + lane, pos, qs + (size_t)h * hd, scale,
+                                                 a1, a2, biased);
+                p = expf(s - ms[h]) * linv[h];
+            }
+            P[h * TA_TILE + lane] = p;
+        }
+        if (tid < nk) {
+            const int j = j0 + tid;
+            vrow[tid] = (size_t)table[j / page_size] * page_elems + v_off + (size_t)(j % page_size) * vd;
+        }
+        __syncthreads();
+        if (talk) {
+            for (int i = tid; i < nh * TA_TILE; i += TA_THREADS) {
+                const int h = i / TA_TILE, jj = i - h * TA_TILE;
+                float a = 0.f;
+                for (int g = 0; g < nh; ++g) a = fmaf(talk_s[h * nh + g], P[g * TA_TILE + jj], a);
+                PM[i] = a;
+            }
+            __syncthreads();
+        }
+        // the tile's values, weighted: a thread per output element
+        for (int i = tid; i < nh * vd; i += TA_THREADS) {
+            const int h = i / vd, e = i - h * vd;
+            const size_t head_off = (size_t)(h / rep) * page_size * vd + e;
+            const float* pw = PM + h * TA_TILE;
+            float acc = Os[i];
+            for (int jj = 0; jj < nk; ++jj) acc = fmaf(pw[jj], rv_to_float(cache[vrow[jj] + head_off]), acc);
+            Os[i] = acc;
+        }
+        __syncthreads();
+    }
+    for (int i = tid; i < nh * vd; i += TA_THREADS) o[i] = rv_from_float<T>(Os[i]);
+}
+
+static RvPerDevice g_ta_once[4];
+
+template <typename T, bool VEC>
+static int ta_launch(int which, const void* q, const void* cache, const int* block_tables, const int* cu_seqlens, const int* ctx_lens,
+                     const int* token_seq, void* out, int n_tokens, int nh, int nkv, int hd, int vd, int page_size, int max_blocks,
+                     float scale, const float* r1, const float* r2, const float* talk, int chunk, size_t smem, cudaStream_t stream) {
+    const int st = rv_configure_smem(g_ta_once[which], talking_attention_kernel<T, VEC>, 200 * 1024);
+    if (st != RV_OK) return st;
+    RV_LAUNCH_ST = rv_launch(talking_attention_kernel<T, VEC>, dim3(n_tokens), dim3(TA_THREADS), smem, stream, (const T*)q, (const T*)cache,
+                             block_tables, cu_seqlens, ctx_lens, token_seq, (T*)out, nh, nkv, hd, vd, page_size, max_blocks, scale, r1, r2,
+                             talk, chunk);
+    return rv_launch_status();
+}
+
+// q, cache and out share one type (`dtype`); r1 / r2 (both or neither), talk and chunk (<= 0: none) are options.
+RV_EXPORT int rv_talking_attention(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
+                                   const int* ctx_lens, const int* token_seq, void* out, int n_tokens, int nh, int nkv, int hd, int vd,
+                                   int page_size, int max_blocks, float scale, const float* r1, const float* r2, const float* talk,
+                                   int chunk, int dtype, cudaStream_t stream) {
+    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || vd <= 0 || page_size <= 0 || max_blocks <= 0) return RV_ERR_BAD_SIZE;
+    if ((r1 == nullptr) != (r2 == nullptr)) return RV_ERR_BAD_SIZE;
+    if (dtype & ~1) return RV_ERR_BAD_DTYPE;
+    const size_t smem = TA_TILE * sizeof(size_t) +
+                        sizeof(float) * ((size_t)nh * hd + (size_t)nh * vd + 2 * (size_t)nh * TA_TILE + (size_t)nh * nh + 2 * (size_t)nh);
+    if (smem > 200 * 1024) return RV_ERR_UNSUPPORTED;
+    if (n_tokens == 0) return RV_OK;
+    const int el = dtype == RV_DTYPE_F32 ? 4 : 2;
+    const bool vec = (hd * el) % 16 == 0 && (vd * el) % 16 == 0 && ((uintptr_t)cache % 16) == 0;
+#define TA_GO(W, T, V) return ta_launch<T, V>(W, q, cache, block_tables, cu_seqlens, ctx_lens, token_seq, out, n_tokens, nh, nkv, hd, vd, \
+                                              page_size, max_blocks, scale, r1, r2, talk, chunk, smem, stream)
+    if (dtype == RV_DTYPE_F32) {
+        if (vec) TA_GO(0, float, true);
+        TA_GO(1, float, false);
+    }
+    if (vec) TA_GO(2, __nv_bfloat16, true);
+    TA_GO(3, __nv_bfloat16, false);
+#undef TA_GO
+}

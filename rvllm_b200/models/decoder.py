@@ -75,7 +75,9 @@ class DecoderModel:
         out.append((self.spec.final_norm_prefix, self.final_norm))
         for key, pe in self.position_encodings.items():
             out.append((f"position.{key}.", pe))
-        out.extend((f"hooks.embedding.{i}.", h) for i, h in enumerate(self.embedding_hooks))
+        # (a hook that sets `names_in_full` names its tensors as the checkpoint does, without a prefix)
+        out.extend(("" if getattr(h, "names_in_full", False) else f"hooks.embedding.{i}.", h)
+                   for i, h in enumerate(self.embedding_hooks))
         out.extend((f"hooks.logits.{i}.", h) for i, h in enumerate(self.logit_hooks))
         # (a hook in front of a run entry names its tensors in full: several entries may share one)
         out.extend(("", h) for hs in self.entry_hooks for h in hs)

@@ -8,9 +8,10 @@ tensors it owns (`tensor_specs`, names relative to its prefix) and receives them
   tables [max_len, rotary_dim/2] or None; `on_embeddings(x, ctx)` -> x for encodings that act
   on the input of the first layer.
 * norm: `__call__(x, ctx)` -> tensor of the same shape.
-* mixer: `cache_need()` -> `KvCacheNeed`, `StateNeed` or None;
+* mixer: `cache_need()` -> `KvCacheNeed`, `StateNeed`, `CompositeNeed` (several of these, for a mixer
+  made of mixers) or None;
   `__call__(x, ctx, cache, residual, write_cache)` -> residual + mixed x.  `cache` is the
-  `CacheView` of the run entry's cache slot.
+  `CacheView` of the run entry's cache slot (with one sub-view per member of a `CompositeNeed`).
 * feed-forward: `__call__(x, ctx, residual)` -> residual + f(x).
 * block: built from `parts`, the layer's built parts by role name (which roles it needs is the
   block's own matter), plus its parameters; `__call__(x, ctx, cache, write_cache)` -> x.
@@ -41,11 +42,28 @@ class TensorSpec:
 class KvCacheNeed:
     """Paged keys and values; `window` None keeps every key, W keeps the last W.  `planes` is 2 for
     separate key and value rows, 1 for mixers that keep ONE row per token and head from which both are
-    read (a latent that keys and values are projections of)."""
+    read (a latent that keys and values are projections of).  `value_dim`: the size of a value row where it
+    differs from the key's `head_dim` (a page then holds all its key rows followed by all its value rows,
+    and the group's tensor is flat per page).  `chunk` C: a query at position i reads keys of its own block of
+    C positions only (floor(i / C) = floor(j / C)), so pages that lie wholly below the block of the next
+    query are given back."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    value_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def row_elements(self) -> int:
+        """Elements one token keeps per kv head over all planes."""
+        if self.value_dim is None or self.planes != 2:
+            return self.planes * self.head_dim
+        return self.head_dim + self.value_dim
+
+    @property
+    def flat_pages(self) -> bool:
+        return self.planes == 2 and self.value_dim is not None and self.value_dim != self.head_dim
 
 
 @dataclass(frozen=True)
@@ -53,6 +71,13 @@ class StateNeed:
     """State of fixed size per request (shape without the request dimension)."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class CompositeNeed:
+    """What a mixer made of several mixers needs: one entry per member (`KvCacheNeed`, `StateNeed` or None), in
+    the members' order.  The run entry's `CacheView` then carries one sub-view per member in `parts`."""
+    parts: Tuple[object, ...]
 
 
 class Part:

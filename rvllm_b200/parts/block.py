@@ -140,3 +140,45 @@ class SandwichNormResidualBlock:
 
 
 BLOCKS.register("sandwich_norm_residual", SandwichNormResidualBlock)
+
+
+class PreNormStreamResidualBlock:
+    """`prenorm_stream_residual`: x + mixer(norm(x)), then x + feed_forward(norm(x)), on a float32 stream
+    (`ModelSpec.residual_dtype`): the sublayers return float32, the sums are formed in 32 bits, and the kernel that
+    adds a sublayer's result also writes what the next sublayer reads (the new stream under that sublayer's norm, in
+    the activations' type).  A layer may have no feed-forward.  An optional last part `token_input` (a feed-forward
+    by interface: `__call__(x, ctx, residual) -> residual + f(x)`) reads the stream ITSELF, not a normalised copy."""
+    ROLES = ("mixer", "mixer_norm")
+    OPTIONAL = ("feed_forward", "feed_forward_norm", "token_input")
+
+    def __init__(self, parts):
+        from ..errors import ConfigError
+        names = set(parts)
+        if not set(self.ROLES) <= names or not names <= set(self.ROLES + self.OPTIONAL) or \
+                (("feed_forward" in names) != ("feed_forward_norm" in names)):
+            raise ConfigError(f"the pre-norm stream block arranges {', '.join(self.ROLES)} and optionally "
+                              f"{', '.join(self.OPTIONAL)}; got {', '.join(sorted(parts))}")
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.feed_forward, self.feed_forward_norm = parts.get("feed_forward"), parts.get("feed_forward_norm")
+        self.token_input = parts.get("token_input")
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not hasattr(n, "as_rms"):
+                raise ConfigError("the pre-norm stream block needs norms that offer `as_rms()` (an RMSNorm)")
+
+    def __call__(self, x, ctx, cache, write_cache=True):
+        k = ctx.kernels
+        dtype = ctx.extras.get("activation_dtype", x.dtype)
+        if x.dtype != torch.float32:
+            x = x.float()
+        h = k.rmsnorm(x, *self.mixer_norm.as_rms(), out_dtype=dtype)
+        y = self.mixer(h, ctx, cache, residual=None, write_cache=write_cache, out_dtype=torch.float32)
+        if self.feed_forward is not None:
+            x, h = k.stream_add_norm(x, y, self.feed_forward_norm.as_rms(), dtype)
+            y = self.feed_forward(h, ctx, residual=None, out_dtype=torch.float32)
+        if self.token_input is None:
+            return k.stream_add_norm(x, y, None, None)[0]
+        x, h = k.stream_add_norm(x, y, None, dtype)
+        return self.token_input(h, ctx, residual=x)
+
+
+BLOCKS.register("prenorm_stream_residual", PreNormStreamResidualBlock)

@@ -14,10 +14,12 @@ class Linear(Part):
     (fusing after v3/crates/rvllm-loader/src/load_multiformat.rs:372-407, 445-477)."""
 
     def __init__(self, in_features: int, out_features: Sequence[int], names: Sequence[str], bias: bool = False,
-                 suffix: str = ".weight"):
-        """`suffix` follows a matrix's name in the checkpoint (".weight" in most; "" where the name is the tensor)."""
+                 suffix: str = ".weight", bias_suffix: str = ".bias"):
+        """`suffix` follows a matrix's name in the checkpoint (".weight" in most; "" where the name is the tensor),
+        `bias_suffix` the name of its bias."""
         assert len(out_features) == len(names)
         self.suffix = suffix
+        self.bias_suffix = bias_suffix
         self.in_features = in_features
         self.out_features = list(out_features)
         self.names = list(names)
@@ -30,7 +32,7 @@ class Linear(Part):
         for name, n in zip(self.names, self.out_features):
             specs[f"{name}{self.suffix}"] = TensorSpec((n, self.in_features), "matrix")
             if self.has_bias:
-                specs[f"{name}.bias"] = TensorSpec((n,), "bias")
+                specs[f"{name}{self.bias_suffix}"] = TensorSpec((n,), "bias")
         return specs
 
     def bind(self, get) -> None:
@@ -39,7 +41,7 @@ class Linear(Part):
         dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
         self.weight = (ws[0].to(dt) if len(ws) == 1 else torch.cat([w.to(dt) for w in ws], dim=0)).contiguous()
         if self.has_bias:
-            bs = [get(f"{n}.bias") for n in self.names]
+            bs = [get(f"{n}{self.bias_suffix}") for n in self.names]
             bdt = torch.float32 if any(b.dtype == torch.float32 for b in bs) else bs[0].dtype
             self.bias = (bs[0].to(bdt) if len(bs) == 1 else torch.cat([b.to(bdt) for b in bs], dim=0)).contiguous()
 

@@ -1,4 +1,5 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * gamma, plain gamma, arithmetic in float.
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * gamma, arithmetic in float; gamma is the stored weight, or one plus
+the stored weight for checkpoints that keep it around zero (`unit_offset`).
 
 v3/crates/rvllm-fused/src/reference.rs:12-24 and kernels/fused_rmsnorm_fp8_quant.cu:61-84 of
 the reference; eps comes from the configuration (the reference hard-codes 1e-6 in two tails,
@@ -11,10 +12,11 @@ from .base import NORMS, Part, TensorSpec
 
 class RMSNorm(Part):
     """`tensor` is the name of the weight below the part's prefix ("weight" in most checkpoints; "" where the
-    prefix itself names the tensor)."""
+    prefix itself names the tensor).  `unit_offset`: the checkpoint stores gamma - 1; the sum is formed once, in
+    float32, when the tensor is bound."""
 
-    def __init__(self, size: int, eps: float, tensor: str = "weight"):
-        self.size, self.eps, self.tensor = size, eps, tensor
+    def __init__(self, size: int, eps: float, tensor: str = "weight", unit_offset: bool = False):
+        self.size, self.eps, self.tensor, self.unit_offset = size, eps, tensor, unit_offset
         self.weight = None
 
     def tensor_specs(self):
@@ -22,6 +24,8 @@ class RMSNorm(Part):
 
     def bind(self, get):
         self.weight = get(self.tensor)
+        if self.unit_offset:
+            self.weight = (self.weight.float() + 1.0).contiguous()
 
     def __call__(self, x, ctx):
         return ctx.kernels.rmsnorm(x, self.weight, self.eps)

@@ -126,9 +126,12 @@ class EmulatedKernels:
                 out[t] += weight * (down[e].float() @ (g / (1.0 + torch.exp(-g)) * u).to(x.dtype).float())
         return out.to(out_dtype or x.dtype)
 
-    def act_mul(self, gate_up, activation, out_dtype=None):
+    def act_mul(self, gate_up, activation, out_dtype=None, limit=None, alpha=None):
         inter = gate_up.shape[1] // 2
         g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+        if activation == "swiglu_clamp":
+            g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+            return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out_dtype or gate_up.dtype)
         if activation == "silu":
             a = g / (1.0 + torch.exp(-g))
         else:
@@ -281,6 +284,153 @@ class EmulatedKernels:
                         o = o * gate[t, h]
                     out[t, h] = o.to(q.dtype)
         return out.view(T, num_heads * head_dim)
+
+    # ---- the kernels of the pre-norm stream block, the mamba1 mixer, the attention that mixes its weights across heads
+    # ---- and the gated delta rule
+    def scale_add_sinusoid(self, x, positions, frequencies, scale):
+        ang = positions.double()[:, None] * frequencies.double()[None, :]
+        pe = torch.stack([torch.sin(ang), torch.cos(ang)], dim=-1).reshape(x.shape[0], -1)[:, :x.shape[1]]
+        return (x.double() * scale + pe).float()
+
+    def stream_add_norm(self, x, y, norm, out_dtype):
+        if y is not None:
+            x += y
+        if out_dtype is None:
+            return x, None
+        if norm is None:
+            return x, x.to(out_dtype)
+        return x, self.rmsnorm(x, norm[0], norm[1]).to(out_dtype)
+
+    def gelu_mul_columns(self, g, table_rows, col0, out_dtype):
+        gf = g.float()
+        a = 0.5 * gf * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (gf + 0.044715 * gf ** 3)))
+        return (a * table_rows[:, col0:col0 + g.shape[1]].float()).to(out_dtype)
+
+    def column_slice(self, x, col0, n, out_dtype):
+        return x[:, col0:col0 + n].to(out_dtype).contiguous()
+
+    def scaled_sum(self, a, sa, b, sb):
+        if a is None:
+            return b.float() * sb
+        a.mul_(sa).add_(b.float() * sb)
+        return a
+
+    def selective_scan(self, u, dt_raw, dt_bias, a, bc, b_col0, c_col0, d_skip, z, z_col0, cu_seqlens, state_slots, state, out_dtype):
+        T, inner = u.shape
+        N = a.shape[1]
+        uf = u.float()
+        y = torch.zeros((T, inner))
+        cu = cu_seqlens.tolist()
+        for s, slot in enumerate(state_slots.tolist()):
+            if slot < 0:
+                continue
+            S = state[slot, :inner * N].view(inner, N)
+            for t in range(cu[s], cu[s + 1]):
+                dt = torch.nn.functional.softplus(dt_raw[t].float() + dt_bias, threshold=20.0)
+                B, C = bc[t, b_col0:b_col0 + N].float(), bc[t, c_col0:c_col0 + N].float()
+                S.copy_(torch.exp(dt[:, None] * a) * S + (dt * uf[t])[:, None] * B[None, :])
+                y[t] = S @ C + d_skip * uf[t]
+        zf = z[:, z_col0:z_col0 + inner].float()
+        return (y * zf / (1.0 + torch.exp(-zf))).to(out_dtype)
+
+    @staticmethod
+    def _kv_planes(cache_layer, G, ps, d, vd):
+        """Views [pages, G, page, d] and [pages, G, page, vd] of a cache layer in either layout."""
+        flat = cache_layer.reshape(cache_layer.shape[0], -1)
+        nk = G * ps * d
+        return flat[:, :nk].view(-1, G, ps, d), flat[:, nk:nk + G * ps * vd].view(-1, G, ps, vd)
+
+    def kv_prepare(self, proj, slot_mapping, cache_layer, num_heads, num_kv_heads, head_dim, value_dim, value_norm_eps, out_dtype,
+                   write_kv=True):
+        T = proj.shape[0]
+        qw, kw = num_heads * head_dim, num_kv_heads * head_dim
+        x = proj.float()
+        if write_kv:
+            ps = cache_layer.numel() // cache_layer.shape[0] // (num_kv_heads * (head_dim + value_dim))
+            K, V = self._kv_planes(cache_layer, num_kv_heads, ps, head_dim, value_dim)
+            k = x[:, qw:qw + kw].view(T, num_kv_heads, head_dim)
+            v = x[:, qw + kw:].view(T, num_kv_heads, value_dim)
+            if value_norm_eps is not None:
+                v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + value_norm_eps)
+            for t, slot in enumerate(slot_mapping.tolist()):
+                if slot < 0:
+                    continue
+                K[slot // ps, :, slot % ps] = k[t].to(cache_layer.dtype)
+                V[slot // ps, :, slot % ps] = v[t].to(cache_layer.dtype)
+        return x[:, :qw].to(out_dtype).contiguous()
+
+    def talking_attention(self, q, cache_layer, meta, positions, num_heads, num_kv_heads, head_dim, value_dim, scale, r1, r2,
+                          talk, chunk):
+        T = q.shape[0]
+        ps = meta.page_size
+        K, V = self._kv_planes(cache_layer, num_kv_heads, ps, head_dim, value_dim)
+        out = torch.zeros((T, num_heads, value_dim))
+        qv = q.view(T, num_heads, head_dim).float()
+        cu = meta.cu_seqlens.tolist()
+        rep = num_heads // num_kv_heads
+        for s in range(meta.num_seqs):
+            ctx = int(meta.ctx_lens[s])
+            if ctx <= 0:
+                continue
+            q_len = cu[s + 1] - cu[s]
+            table = meta.block_tables[s].tolist()
+            for i in range(q_len):
+                t = cu[s] + i
+                pos = ctx - q_len + i
+                assert pos == int(positions[t])
+                lo = (pos // chunk) * chunk if chunk else 0
+                keys = list(range(lo, pos + 1))
+                pages = [table[j // ps] for j in keys]
+                assert all(p >= 0 for p in pages), "attention reads a page that was given back"
+                offs = [j % ps for j in keys]
+                dist = torch.tensor([pos - j for j in keys], dtype=torch.float32)
+                P = torch.zeros((num_heads, len(keys)))
+                for h in range(num_heads):
+                    sc = (K[pages, h // rep, offs, :].float() @ qv[t, h]) * scale
+                    if r1 is not None:
+                        sc = sc - r1[h] * torch.log1p(r2[h] * dist)
+                    P[h] = torch.softmax(sc, 0)
+                if talk is not None:
+                    P = talk.float() @ P
+                for h in range(num_heads):
+                    out[t, h] = P[h] @ V[pages, h // rep, offs, :].float()
+        return out.view(T, num_heads * value_dim).to(q.dtype)
+
+    def delta_rule(self, qkv, proj, b_col0, a_col0, a_log, dt_bias, cu_seqlens, state_slots, state, heads, qk_heads, head_dim,
+                   value_dim, unit_eps):
+        T = qkv.shape[0]
+        qk = qk_heads * head_dim
+        x = qkv.float()
+        q = x[:, :qk].view(T, qk_heads, head_dim)
+        k = x[:, qk:2 * qk].view(T, qk_heads, head_dim)
+        v = x[:, 2 * qk:].view(T, heads, value_dim)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * head_dim ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+        rep = heads // qk_heads
+        beta = torch.sigmoid(proj[:, b_col0:b_col0 + heads].float())
+        g = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(proj[:, a_col0:a_col0 + heads].float() + dt_bias, threshold=20.0))
+        o = torch.zeros((T, heads, value_dim))
+        cu = cu_seqlens.tolist()
+        for s, slot in enumerate(state_slots.tolist()):
+            if slot < 0:
+                continue
+            S = state[slot, :heads * head_dim * value_dim].view(heads, head_dim, value_dim)
+            for t in range(cu[s], cu[s + 1]):
+                for h in range(heads):
+                    kh, qh = k[t, h // rep], q[t, h // rep]
+                    Sh = g[t, h] * S[h]
+                    u = beta[t, h] * (v[t, h] - Sh.t() @ kh)
+                    Sh = Sh + kh[:, None] * u[None, :]
+                    S[h] = Sh
+                    o[t, h] = Sh.t() @ qh
+        return o.view(T, heads * value_dim)
+
+    def head_norm_gate(self, o, gamma, eps, proj, g_col0, heads, value_dim, out_dtype):
+        T = o.shape[0]
+        of = o.float().view(T, heads, value_dim)
+        of = of / torch.sqrt((of * of).mean(-1, keepdim=True) + eps) * gamma.float()
+        z = proj[:, g_col0:g_col0 + heads * value_dim].float().view(T, heads, value_dim)
+        return (of * z / (1.0 + torch.exp(-z))).reshape(T, heads * value_dim).to(out_dtype)
 
     def linear(self, x, weight, bias=None, residual=None, out_dtype=None, norm=None):
         if norm is not None:
