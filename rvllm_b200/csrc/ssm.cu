@@ -628,3 +628,145 @@ RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw
                              (size_t)state_stride, out, out_dtype, inner, N, parts);
     return rv_launch_status();
 }
+
+// ------------------------------------------------------------------ the gated delta rule
+// Per value head h, with S of size d x vd (d: key size, vd: value size) kept as [heads][d][vd] at offset 0 of the request's
+// state row:
+//     q <- q / sqrt(sum q^2 + unit_eps) d^(-1/2),   k <- k / sqrt(sum k^2 + unit_eps)          (q/k head h / (heads / qk_heads))
+//     beta = sigmoid(b),   g = exp(-exp(A_log_h) softplus(a + dt_bias_h))
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// Every step of the rule acts on the columns of S one by one, so a column is one thread's work (no exchange between
+// columns): a column's d entries live in the registers of `parts` neighbouring lanes, DR_NS each, whose partial sums
+// meet by shuffles.  Grid (column blocks, heads, sequences), 128 threads.  The unit vectors q and k of DR_CHUNK tokens, and
+// the tokens' g and beta, wait in shared memory; a lane's DR_NS entries of a row start at a multiple of DR_NS + 4 floats, so
+// that the 16-byte reads of the `parts` lanes of a column fall on different banks.  Rows are zero beyond d.
+#define DR_NS 32
+#define DR_PAD (DR_NS + 4)
+#define DR_CHUNK 16
+
+__global__ void __launch_bounds__(128)
+delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, const float* __restrict__ proj, int proj_stride,
+                  int b_col0, int a_col0, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                  const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, float* __restrict__ state,
+                  size_t state_stride, float* __restrict__ out, int heads, int qk_heads, int d, int vd, int parts, float unit_eps) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ __align__(16) float dr_smem[];
+    const int seq = blockIdx.z, h = blockIdx.y;
+    const int slot = state_slots[seq];
+    if (slot < 0) return;
+    const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
+    const int row_floats = parts * DR_PAD;
+    float* sQ = dr_smem;                                   // [DR_CHUNK][row_floats]
+    float* sK = sQ + DR_CHUNK * row_floats;
+    float* sG = sK + DR_CHUNK * row_floats;                // [DR_CHUNK]
+    float* sBeta = sG + DR_CHUNK;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per_block = 128 / parts;
+    const int col = blockIdx.x * per_block + tid / parts;
+    const int part = tid % parts;
+    const bool live = col < vd;
+    const int n0 = part * DR_NS;
+    const int kh = h / (heads / qk_heads);
+    const int qk = qk_heads * d;
+    const float q_scale = rsqrtf((float)d);
+    float S[DR_NS];
+    float* srow = state + (size_t)slot * state_stride + (size_t)h * d * vd;
+#pragma unroll
+    for (int i = 0; i < DR_NS; ++i) S[i] = (live && n0 + i < d) ? srow[(size_t)(n0 + i) * vd + col] : 0.f;
+    for (int i = tid; i < 2 * DR_CHUNK * row_floats; i += 128) dr_smem[i] = 0.f;      // the padding stays zero from here on
+    const float decay_rate = expf(a_log[h]), a_bias = dt_bias[h];
+    for (int t0 = 0; t0 < n_tok; t0 += DR_CHUNK) {
+        const int nt = min(DR_CHUNK, n_tok - t0);
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += 4) {                       // a warp per token: q and k of the head, made unit vectors
+            const size_t row = (size_t)(start + t0 + tt) * qkv_stride;
+            float sq = 0.f, sk = 0.f;
+            for (int e = lane; e < d; e += 32) {
+                const float qv = rv_load_any(qkv, qkv_dtype, row + (size_t)kh * d + e);
+                const float kv = rv_load_any(qkv, qkv_dtype, row + qk + (size_t)kh * d + e);
+                const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                sQ[at] = qv;
+                sK[at] = kv;
+                sq = fmaf(qv, qv, sq);
+                sk = fmaf(kv, kv, sk);
+            }
+            sq = rv_warp_sum(sq);
+            sk = rv_warp_sum(sk);
+            const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
+            for (int e = lane; e < d; e += 32) {                      // every lane rescales what it wrote itself
+                const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                sQ[at] *= rq;
+                sK[at] *= rk;
+            }
+        }
+        if (tid < nt) {
+            const size_t row = (size_t)(start + t0 + tid) * proj_stride;
+            const float b = proj[row + b_col0 + h];
+            const float a = proj[row + a_col0 + h] + a_bias;
+            const float sp = a > 20.f ? a : log1pf(expf(a));
+            sBeta[tid] = 1.0f / (1.0f + expf(-b));
+            sG[tid] = expf(-decay_rate * sp);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {                   // (threads beyond the last column walk along: the shuffles need every lane)
+            const size_t trow = (size_t)(start + t0 + tt);
+            const float4* K4 = reinterpret_cast<const float4*>(sK + tt * row_floats + part * DR_PAD);
+            const float4* Q4 = reinterpret_cast<const float4*>(sQ + tt * row_floats + part * DR_PAD);
+            const float vv = live ? rv_load_any(qkv, qkv_dtype, trow * qkv_stride + 2 * qk + (size_t)h * vd + col) : 0.f;
+            float kreg[DR_NS];
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < DR_NS / 4; ++i) {
+                const float4 k4 = K4[i];
+                kreg[4 * i] = k4.x; kreg[4 * i + 1] = k4.y; kreg[4 * i + 2] = k4.z; kreg[4 * i + 3] = k4.w;
+                acc = fmaf(S[4 * i], k4.x, acc); acc = fmaf(S[4 * i + 1], k4.y, acc);
+                acc = fmaf(S[4 * i + 2], k4.z, acc); acc = fmaf(S[4 * i + 3], k4.w, acc);
+            }
+            for (int o = 1; o < parts; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            const float g = sG[tt];
+            const float u = sBeta[tt] * (vv - g * acc);
+            float ov = 0.f;
+#pragma unroll
+            for (int i = 0; i < DR_NS / 4; ++i) {
+                const float4 q4 = Q4[i];
+                S[4 * i] = fmaf(g, S[4 * i], kreg[4 * i] * u);             ov = fmaf(S[4 * i], q4.x, ov);
+                S[4 * i + 1] = fmaf(g, S[4 * i + 1], kreg[4 * i + 1] * u); ov = fmaf(S[4 * i + 1], q4.y, ov);
+                S[4 * i + 2] = fmaf(g, S[4 * i + 2], kreg[4 * i + 2] * u); ov = fmaf(S[4 * i + 2], q4.z, ov);
+                S[4 * i + 3] = fmaf(g, S[4 * i + 3], kreg[4 * i + 3] * u); ov = fmaf(S[4 * i + 3], q4.w, ov);
+            }
+            for (int o = 1; o < parts; o <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
+            if (part == 0 && live) out[trow * heads * vd + (size_t)h * vd + col] = ov;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DR_NS; ++i)
+            if (n0 + i < d) srow[(size_t)(n0 + i) * vd + col] = S[i];
+    }
+}
+
+// qkv rows: [q: qk_heads x d | k: qk_heads x d | v: heads x vd] (after the convolution); the logits of beta and of the
+// decay are float columns b_col0 .. and a_col0 .. of `proj`; out: float [tokens, heads x vd].
+RV_EXPORT int rv_delta_rule(const void* qkv, int qkv_dtype, int qkv_stride, const float* proj, int proj_stride, int b_col0,
+                            int a_col0, const float* a_log, const float* dt_bias, const int* cu_seqlens, const int* state_slots,
+                            float* state, long long state_stride, float* out, int n_seqs, int heads, int qk_heads, int d, int vd,
+                            float unit_eps, cudaStream_t stream) {
+    if (n_seqs < 0 || heads <= 0 || qk_heads <= 0 || heads % qk_heads || d <= 0 || d > 32 * DR_NS || vd <= 0 || n_seqs > 65535 ||
+        heads > 65535)
+        return RV_ERR_BAD_SIZE;
+    if (qkv_stride < 2 * qk_heads * d + heads * vd || b_col0 < 0 || a_col0 < 0 || b_col0 + heads > proj_stride ||
+        a_col0 + heads > proj_stride || state_stride < (long long)heads * d * vd)
+        return RV_ERR_BAD_SIZE;
+    if (qkv_dtype & ~1) return RV_ERR_BAD_DTYPE;
+    if (n_seqs == 0) return RV_OK;
+    int parts = 1;
+    while (parts * DR_NS < d) parts <<= 1;             // a power of two of at most 32 lanes of one warp
+    const int per_block = 128 / parts;
+    const size_t smem = sizeof(float) * (2 * (size_t)DR_CHUNK * parts * DR_PAD + 2 * DR_CHUNK);
+    if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
+    RV_LAUNCH_ST = rv_launch(delta_rule_kernel, dim3((vd + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, qkv,
+                             qkv_dtype, qkv_stride, proj, proj_stride, b_col0, a_col0, a_log, dt_bias, cu_seqlens, state_slots, state,
+                             (size_t)state_stride, out, heads, qk_heads, d, vd, parts, unit_eps);
+    return rv_launch_status();
+}

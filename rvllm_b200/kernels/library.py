@@ -883,15 +883,25 @@ class CudaKernels:
 
     ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 
-    def act_mul(self, gate_up: torch.Tensor, activation: str, out_dtype=None) -> torch.Tensor:
-        """rows [gate | up] -> act(gate) * up, computed in float."""
+    def act_mul(self, gate_up: torch.Tensor, activation: str, out_dtype=None, limit: Optional[float] = None,
+                alpha: Optional[float] = None) -> torch.Tensor:
+        """rows [gate | up] -> act(gate) * up, computed in float.  "swiglu_clamp": g sigmoid(alpha g) (u + 1) with
+        g = min(gate, limit), u = clamp(up, -limit, limit)."""
         _need(gate_up, "gate_up", dims=2)
-        if activation not in self.ACTIVATIONS:
-            raise KernelError(f"act_mul: activation {activation!r} is not known ({', '.join(self.ACTIVATIONS)})")
+        if activation not in self.ACTIVATIONS and activation != "swiglu_clamp":
+            raise KernelError(f"act_mul: activation {activation!r} is not known ({', '.join(self.ACTIVATIONS)}, swiglu_clamp)")
         inter = gate_up.shape[1] // 2
         if inter * 2 != gate_up.shape[1]:
             raise KernelError(f"act_mul: row width {gate_up.shape[1]} is odd")
         out = torch.empty((gate_up.shape[0], inter), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
+        if activation == "swiglu_clamp":
+            if limit is None or alpha is None:
+                raise KernelError("act_mul: swiglu_clamp needs `limit` and `alpha`")
+            st = self._lib("streamops.cu").rv_act_mul_clamp(_ptr(gate_up), c_int(self._dt(gate_up, "gate_up")), _ptr(out),
+                                                           c_int(self._dt(out, "out")), c_int(gate_up.shape[0]), c_int(inter),
+                                                           c_float(limit), c_float(alpha), self._stream())
+            _check("act_mul", st)
+            return out
         st = self._lib("rowops.cu").rv_act_mul(_ptr(gate_up), c_int(self._dt(gate_up, "gate_up")), _ptr(out), c_int(self._dt(out, "out")),
                                                c_int(gate_up.shape[0]), c_int(inter), c_int(self.ACTIVATIONS[activation]), self._stream())
         _check("act_mul", st)
@@ -1047,6 +1057,199 @@ class CudaKernels:
         st = self._lib("rowops.cu").rv_softcap(_ptr(logits), c_float(cap), ctypes.c_longlong(logits.numel()), self._stream())
         _check("softcap", st)
         return logits
+
+    # ------------------------------------------------------------------ float32 stream of pre-norm layers, small steps around mixers
+    def scale_add_sinusoid(self, x, positions, frequencies, scale: float) -> torch.Tensor:
+        """x * scale + pe(position), pe[2i] = sin(p w_i), pe[2i + 1] = cos(p w_i); `frequencies`: float64 w_i.  Float32 result."""
+        _need(x, "x", dims=2); _need(positions, "positions", torch.int32, 1); _need(frequencies, "frequencies", torch.float64, 1)
+        rows, cols = x.shape
+        if positions.shape[0] != rows or frequencies.shape[0] != (cols + 1) // 2:
+            raise KernelError(f"scale_add_sinusoid: {positions.shape[0]} positions and {frequencies.shape[0]} frequencies for {tuple(x.shape)}")
+        out = torch.empty((rows, cols), dtype=torch.float32, device=x.device)
+        st = self._lib("streamops.cu").rv_scale_add_sinusoid(_ptr(x), c_int(self._dt(x, "x")), _ptr(positions), _ptr(frequencies),
+                                                            c_float(scale), _ptr(out), c_int(rows), c_int(cols), self._stream())
+        _check("scale_add_sinusoid", st)
+        return out
+
+    def stream_add_norm(self, x, y: Optional[torch.Tensor], norm, out_dtype):
+        """x += y on the float32 stream, in place (y None: nothing is added).  Returns (x, second result): None without
+        `out_dtype`; the new x in `out_dtype`; or, with norm = (gamma, eps), the new x / sqrt(mean(x^2) + eps) * gamma."""
+        _need(x, "x", torch.float32, 2)
+        rows, cols = x.shape
+        if y is not None:
+            _need(y, "y", torch.float32, 2)
+            if y.shape != x.shape:
+                raise KernelError(f"stream_add_norm: {tuple(y.shape)} added to {tuple(x.shape)}")
+        if out_dtype is None and y is None:
+            return x, None
+        gamma, eps = (norm if norm is not None else (None, 0.0))
+        if gamma is not None:
+            _need(gamma, "gamma", dims=1)
+            if gamma.shape[0] != cols:
+                raise KernelError(f"stream_add_norm: gamma has {gamma.shape[0]} entries for rows of {cols}")
+        rounded = torch.empty((rows, cols), dtype=out_dtype, device=x.device) if out_dtype is not None else None
+        st = self._lib("streamops.cu").rv_stream_add_norm(
+            _ptr(x), _ptr(y), _ptr(gamma), c_int(self._dt(gamma, "gamma") if gamma is not None else 0), _ptr(rounded),
+            c_int(_DT[out_dtype] if rounded is not None else 0), c_int(rows), c_int(cols), c_float(eps), self._stream())
+        _check("stream_add_norm", st)
+        return x, rounded
+
+    def gelu_mul_columns(self, g, table_rows, col0: int, out_dtype) -> torch.Tensor:
+        """gelu_tanh(g[t, c]) * table_rows[t, col0 + c]."""
+        _need(g, "g", dims=2); _need(table_rows, "table_rows", dims=2)
+        rows, cols = g.shape
+        if table_rows.shape[0] != rows or col0 < 0 or col0 + cols > table_rows.shape[1]:
+            raise KernelError(f"gelu_mul_columns: columns {col0}..{col0 + cols} of rows {tuple(table_rows.shape)} for {tuple(g.shape)}")
+        out = torch.empty((rows, cols), dtype=out_dtype, device=g.device)
+        st = self._lib("streamops.cu").rv_gelu_mul_columns(_ptr(g), c_int(self._dt(g, "g")), _ptr(table_rows),
+                                                          c_int(self._dt(table_rows, "table_rows")), c_int(table_rows.shape[1]), c_int(col0),
+                                                          _ptr(out), c_int(_DT[out_dtype]), c_int(rows), c_int(cols), self._stream())
+        _check("gelu_mul_columns", st)
+        return out
+
+    def column_slice(self, x, col0: int, n: int, out_dtype) -> torch.Tensor:
+        """A contiguous copy of columns col0 .. col0 + n of x, in `out_dtype`."""
+        _need(x, "x", dims=2)
+        if col0 < 0 or n <= 0 or col0 + n > x.shape[1]:
+            raise KernelError(f"column_slice: columns {col0}..{col0 + n} of rows of {x.shape[1]}")
+        out = torch.empty((x.shape[0], n), dtype=out_dtype, device=x.device)
+        st = self._lib("streamops.cu").rv_column_slice(_ptr(x), c_int(self._dt(x, "x")), c_int(x.shape[1]), c_int(col0), _ptr(out),
+                                                      c_int(_DT[out_dtype]), c_int(x.shape[0]), c_int(n), self._stream())
+        _check("column_slice", st)
+        return out
+
+    def scaled_sum(self, a: Optional[torch.Tensor], sa: float, b, sb: float) -> torch.Tensor:
+        """a <- sa * a + sb * b in place (float32); a None: a new tensor sb * b."""
+        _need(b, "b", torch.float32)
+        if a is not None:
+            _need(a, "a", torch.float32)
+            if a.shape != b.shape:
+                raise KernelError(f"scaled_sum: {tuple(a.shape)} and {tuple(b.shape)}")
+        out = a if a is not None else torch.empty_like(b)
+        st = self._lib("streamops.cu").rv_scaled_sum(_ptr(a), c_float(sa), _ptr(b), c_float(sb), _ptr(out), ctypes.c_longlong(b.numel()),
+                                                    self._stream())
+        _check("scaled_sum", st)
+        return out
+
+    def head_norm_gate(self, o, gamma, eps: float, proj, g_col0: int, heads: int, value_dim: int, out_dtype) -> torch.Tensor:
+        """Per head: o / sqrt(mean(o^2) + eps) * gamma * silu(z); gamma [value_dim] is shared by the heads, z = columns
+        g_col0 .. g_col0 + heads * value_dim of `proj`."""
+        _need(o, "o", torch.float32, 2); _need(gamma, "gamma", dims=1); _need(proj, "proj", dims=2)
+        rows = o.shape[0]
+        if o.shape[1] != heads * value_dim or gamma.shape[0] != value_dim or proj.shape[0] != rows or g_col0 + heads * value_dim > proj.shape[1]:
+            raise KernelError("head_norm_gate: shapes of o, gamma and the gate do not agree")
+        out = torch.empty((rows, heads * value_dim), dtype=out_dtype, device=o.device)
+        st = self._lib("streamops.cu").rv_head_norm_gate(_ptr(o), _ptr(gamma), c_int(self._dt(gamma, "gamma")), _ptr(proj),
+                                                        c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), c_int(g_col0), _ptr(out),
+                                                        c_int(_DT[out_dtype]), c_int(rows), c_int(heads), c_int(value_dim), c_float(eps),
+                                                        self._stream())
+        _check("head_norm_gate", st)
+        return out
+
+    # ------------------------------------------------------------------ recurrences with one state row per channel / per head
+    def selective_scan(self, u, dt_raw, dt_bias, a, bc, b_col0: int, c_col0: int, d_skip, z, z_col0: int, cu_seqlens, state_slots,
+                       state, out_dtype) -> torch.Tensor:
+        """S[c, n] <- exp(dt_c a[c, n]) S[c, n] + dt_c u_c B_n; y_c = sum_n S[c, n] C_n + D_c u_c; returns y * silu(z) in
+        `out_dtype`.  dt = softplus(dt_raw + dt_bias) per channel; B and C are float columns b_col0 .. and c_col0 .. of `bc`,
+        z columns z_col0 .. of `z`; S lives as [inner][N] at offset 0 of the request's row of `state`."""
+        _need(u, "u", dims=2); _need(dt_raw, "dt_raw", torch.float32, 2); _need(bc, "bc", torch.float32, 2); _need(z, "z", dims=2)
+        _need(a, "a", torch.float32, 2); _need(state, "state", torch.float32, 2)
+        T, inner = u.shape
+        N = a.shape[1]
+        for name, p in (("dt_bias", dt_bias), ("d_skip", d_skip)):
+            _need(p, name, torch.float32, 1)
+            if p.shape[0] != inner:
+                raise KernelError(f"selective_scan: {name} has {p.shape[0]} entries for {inner} channels")
+        if a.shape[0] != inner or dt_raw.shape != (T, inner) or bc.shape[0] != T or z.shape[0] != T:
+            raise KernelError("selective_scan: shapes of u, dt, a, B | C and z do not agree")
+        out = torch.empty((T, inner), dtype=out_dtype, device=u.device)
+        st = self._lib("ssm.cu").rv_selective_scan1(
+            _ptr(u), c_int(self._dt(u, "u")), _ptr(dt_raw), _ptr(dt_bias), _ptr(a), _ptr(bc), c_int(bc.shape[1]), c_int(b_col0),
+            c_int(c_col0), _ptr(d_skip), _ptr(z), c_int(self._dt(z, "z")), c_int(z.shape[1]), c_int(z_col0), _ptr(cu_seqlens),
+            _ptr(state_slots), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(out), c_int(_DT[out_dtype]),
+            c_int(state_slots.shape[0]), c_int(inner), c_int(N), self._stream())
+        _check("selective_scan", st)
+        return out
+
+    def delta_rule(self, qkv, proj, b_col0: int, a_col0: int, a_log, dt_bias, cu_seqlens, state_slots, state, heads: int,
+                   qk_heads: int, head_dim: int, value_dim: int, unit_eps: float) -> torch.Tensor:
+        """The gated delta rule over the step's tokens, continued from and leaving behind each request's S ([heads][head_dim]
+        [value_dim] at offset 0 of its row of `state`).  qkv rows: [q | k | v] after their convolution; the logits of beta and
+        of the decay are float columns b_col0 .. and a_col0 .. of `proj`.  Returns o float32 [T, heads * value_dim]."""
+        _need(qkv, "qkv", dims=2); _need(proj, "proj", torch.float32, 2); _need(state, "state", torch.float32, 2)
+        _need(a_log, "a_log", torch.float32, 1); _need(dt_bias, "dt_bias", torch.float32, 1)
+        T = qkv.shape[0]
+        if qkv.shape[1] != 2 * qk_heads * head_dim + heads * value_dim or proj.shape[0] != T or a_log.shape[0] != heads or \
+                dt_bias.shape[0] != heads:
+            raise KernelError("delta_rule: shapes of q | k | v, the logits and the heads' constants do not agree")
+        out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=qkv.device)
+        st = self._lib("ssm.cu").rv_delta_rule(
+            _ptr(qkv), c_int(self._dt(qkv, "qkv")), c_int(qkv.shape[1]), _ptr(proj), c_int(proj.shape[1]), c_int(b_col0), c_int(a_col0),
+            _ptr(a_log), _ptr(dt_bias), _ptr(cu_seqlens), _ptr(state_slots), _ptr(state), ctypes.c_longlong(state.shape[1]), _ptr(out),
+            c_int(state_slots.shape[0]), c_int(heads), c_int(qk_heads), c_int(head_dim), c_int(value_dim), c_float(unit_eps),
+            self._stream())
+        _check("delta_rule", st)
+        return out
+
+    # ------------------------------------------------------------------ attention whose weights are mixed across the heads
+    @staticmethod
+    def _flat_page_size(cache_layer, num_kv_heads: int, head_dim: int, value_dim: int) -> int:
+        per_page = cache_layer.numel() // cache_layer.shape[0]
+        ps, rest = divmod(per_page, num_kv_heads * (head_dim + value_dim))
+        if rest or ps <= 0:
+            raise KernelError(f"a cache layer of shape {tuple(cache_layer.shape)} does not hold pages of {num_kv_heads} kv heads "
+                              f"with keys of {head_dim} and values of {value_dim}")
+        return ps
+
+    def kv_prepare(self, proj, slot_mapping, cache_layer, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                   value_norm_eps: Optional[float], out_dtype, write_kv: bool = True) -> torch.Tensor:
+        """proj rows [q | k | v]: returns q in `out_dtype`; k and v go into the token's cache slot, v first divided by its
+        root mean square per head when `value_norm_eps` is given.  A page holds its key rows [kv heads][page][head_dim]
+        and behind them its value rows [kv heads][page][value_dim]."""
+        _need(proj, "proj", dims=2)
+        T = proj.shape[0]
+        qw = num_heads * head_dim
+        if proj.shape[1] != qw + num_kv_heads * (head_dim + value_dim):
+            raise KernelError(f"kv_prepare: rows of {proj.shape[1]} columns, expected {qw} + {num_kv_heads} x ({head_dim} + {value_dim})")
+        ps = 1
+        if write_kv:
+            _need(cache_layer, "cache_layer"); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+            ps = self._flat_page_size(cache_layer, num_kv_heads, head_dim, value_dim)
+        q = torch.empty((T, qw), dtype=out_dtype, device=proj.device)
+        st = self._lib("talking_attention.cu").rv_kv_prepare(
+            _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), _ptr(slot_mapping if write_kv else None),
+            _ptr(cache_layer if write_kv else None), c_int(self._dt(cache_layer, "cache_layer") if write_kv else 0), _ptr(q),
+            c_int(_DT[out_dtype]), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim), c_int(ps),
+            c_float(value_norm_eps if value_norm_eps is not None else 0.0), c_int(1 if value_norm_eps is not None else 0),
+            c_int(1 if write_kv else 0), self._stream())
+        _check("kv_prepare", st)
+        return q
+
+    def talking_attention(self, q, cache_layer, meta: AttentionMeta, positions, num_heads: int, num_kv_heads: int, head_dim: int,
+                          value_dim: int, scale: float, r1, r2, talk, chunk: Optional[int]) -> torch.Tensor:
+        """softmax attention over the paged cache whose weights are mixed across the heads (`talk` [heads, heads], float32)
+        before they meet the values; r1, r2 (float32 per head): r1 ln(1 + r2 distance) is taken off the scores; `chunk`: a
+        query sees the keys of its own block of that many positions only.  q, cache and result share one type."""
+        _need(q, "q", dims=2); _need(cache_layer, "cache_layer", q.dtype)
+        T = q.shape[0]
+        if q.shape[1] != num_heads * head_dim:
+            raise KernelError(f"talking_attention: q rows of {q.shape[1]} for {num_heads} heads of {head_dim}")
+        ps = self._flat_page_size(cache_layer, num_kv_heads, head_dim, value_dim)
+        if ps != meta.page_size:
+            raise KernelError(f"talking_attention: the cache's pages hold {ps} tokens, the step's tables count {meta.page_size}")
+        for name, p, n in (("r1", r1, num_heads), ("r2", r2, num_heads), ("talk", talk, num_heads * num_heads)):
+            if p is not None:
+                _need(p, name, torch.float32)
+                if p.numel() != n:
+                    raise KernelError(f"talking_attention: {name} has {p.numel()} entries, expected {n}")
+        out = torch.empty((T, num_heads * value_dim), dtype=q.dtype, device=q.device)
+        st = self._lib("talking_attention.cu").rv_talking_attention(
+            _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(meta.token_seq),
+            _ptr(out), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim), c_int(ps),
+            c_int(meta.max_blocks), c_float(scale), _ptr(r1), _ptr(r2), _ptr(talk), c_int(chunk or 0), c_int(self._dt(q, "q")),
+            self._stream())
+        _check("talking_attention", st)
+        return out
 
     # ------------------------------------------------------------------ latent attention
     def latent_prepare(self, proj, c_gamma, eps: float, positions, cos, sin, slot_mapping, cache_layer, num_heads: int,
