@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200: decode tokens per second, prefill, roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape NAME]
-                    [--workload decode|serve|tufirax|vipelix] [--impl ours|reference]
+                    [--workload decode|serve|tufirax|vipelix|tibepel] [--impl ours|reference]
 
 The default run has the layer sizes of Llama-3.1-8B (32 layers, hidden 4096, 32 query heads,
 8 key/value heads of 128, MLP 14336, vocabulary 128256, llama3 rotary scaling) with random
@@ -788,6 +788,216 @@ def run_vipelix(args):
     print(json.dumps(out))
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --workload tibepel: the Tibepel design (chunked attention whose softmax weights are mixed across the heads beside a
+# gated delta rule, mamba1 scans, clamped gated feed-forwards, a per-token side input, a float32 stream) at layer sizes that
+# resemble real models, beside the Tufirax design of this engine - the closest one: attention and state-space layers
+# around a float32 stream - at the same width, heads, feed-forward and depth; then each of the design's own kernels alone
+# beside the like kernel of that path, with the bytes it has to move (or its FLOPs) over its time against the measured peaks.
+# Random weights; its own JSON line.
+TIBEPEL_SIZES = {
+    "2k": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, r_heads=16, r_kv=8, r_dim=128, r_vdim=128, inner=4096, state=16, dt_rank=128,
+               m_heads=64, m_vdim=64, m_state=128, groups=8, rot=64, layers=8),
+    "4k": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, r_heads=32, r_kv=16, r_dim=128, r_vdim=128, inner=8192, state=16, dt_rank=256,
+               m_heads=128, m_vdim=64, m_state=128, groups=8, rot=128, layers=8),
+}
+TIBEPEL_CHUNK = 4096       # positions per attention chunk (the prompts of this workload lie inside one chunk, as in the Tufirax run)
+
+
+def tibepel_pair(size: dict, vocab: int = 32768):
+    """(Tibepel configuration, Tufirax configuration) of equal width, attention heads, feed-forward and depth.  The Tibepel
+    layers alternate side-by-side mixers and mamba1, the Tufirax layers attention and mamba2, each with a feed-forward."""
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
+                              "scale": size["dim"] ** -0.5, "mask": {"size": TIBEPEL_CHUNK}}, "left_scale": 0.7,
+                     "right": {"heads": size["r_heads"], "kv_heads": size["r_kv"], "dim": size["r_dim"], "vdim": size["r_vdim"], "conv": 4},
+                     "right_scale": 0.7},
+           "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0}}
+    mam = {"type": "mamba1", "mixer": {"inner": size["inner"], "state": size["state"], "dt_rank": size["dt_rank"], "conv": 4},
+           "mlp": {"kind": "dense", "ff": size["ff"], "limit": 7.0}}
+    tib = {"architecture": "Tibepel", "width": size["width"], "vocab": vocab, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+           "logit_softcap": 30.0, "token_side": {"dim": 64}, "layers": [par if i % 2 == 0 else mam for i in range(size["layers"])]}
+    tfx = dict(width=size["width"], heads=size["heads"], kv_heads=size["kv_heads"], dim=size["dim"], rot=size["rot"], ff=size["ff"],
+               m_heads=size["m_heads"], m_vdim=size["m_vdim"], state=size["m_state"], groups=size["groups"], layers=size["layers"])
+    return tib, tufirax_pair(tfx, vocab)[0]
+
+
+def run_tibepel(args):
+    import torch
+
+    from rvllm_b200 import LLM, config_from_dict
+    from rvllm_b200.engine import StepEntry
+    from rvllm_b200.kernels import AttentionMeta
+
+    peaks = measured_peaks()
+    PROMPT, CTX, batch = 2048, 4096, args.batch
+    gen = torch.Generator().manual_seed(0)
+    out = {"workload": "tibepel", "dtype": "bf16", "data": "synthetic", "peaks": peaks["source"], "prompt_len": PROMPT, "batch": batch,
+           "steps": args.steps, "warmup": args.warmup, "models": {}, "kernels": {}}
+
+    def measure(cfg_dict):
+        config = config_from_dict(cfg_dict)
+        llm = LLM(config=config, random_weights=True, seed=0, dtype="bfloat16", block_size=16, num_blocks=batch * (CTX // 16) + 8,
+                  max_model_len=CTX, max_num_seqs=batch, max_num_batched_tokens=PROMPT, enforce_eager=args.eager)
+        runner, V = llm.engine.runner, llm.engine.spec.vocab_size
+        p = torch.randint(0, V, (PROMPT,), generator=gen).tolist()
+        for _ in range(3):
+            runner.step([StepEntry("w", p, [PROMPT - 1])])
+            runner.finish("w")
+        torch.cuda.synchronize()
+        pf = []
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step([StepEntry("p", p, [PROMPT - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.finish("p")
+            pf.append(a.elapsed_time(b))
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, torch.randint(0, V, (PROMPT,), generator=gen).tolist(), [])])
+        for _ in range(args.warmup):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        for rid in ids:
+            runner.finish(rid)
+        kernels = llm.engine.kernels
+        kernels.raise_on_abort()
+        del llm
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(min(pf), 3), "prefill_tok_s": round(PROMPT / (min(pf) / 1e3), 1),
+                "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms / 1e3), 1)}, kernels
+
+    K = None
+    for name in (args.sizes.split(",") if args.sizes else list(TIBEPEL_SIZES)):
+        tib, tfx = tibepel_pair(TIBEPEL_SIZES[name])
+        a, K = measure(tib)
+        b, K = measure(tfx)
+        out["models"][name] = {"tibepel": a, "tufirax_same_size": b, "layers": TIBEPEL_SIZES[name]["layers"],
+                               "prefill_ratio": round(a["prefill_tok_s"] / b["prefill_tok_s"], 3),
+                               "decode_ratio": round(a["decode_tok_s"] / b["decode_tok_s"], 3)}
+    if K is None:
+        from rvllm_b200.kernels import get_library
+        K = get_library("cuda:0")
+
+    # ---- the design's kernels alone, at the "4k" sizes, beside the like kernel of the Tufirax path ----------------
+    z = TIBEPEL_SIZES["4k"]
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bw, peak = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+
+    def by_bytes(name, ms, nbytes, like=None):
+        out["kernels"][name] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / (ms / 1e3) / bw, 3)}
+        if like is not None:
+            out["kernels"][name]["like"] = like
+
+    def like_bytes(kernel, ms, nbytes):
+        return {"kernel": kernel, "ms": round(ms, 4), "frac_hbm": round(nbytes / (ms / 1e3) / bw, 3)}
+
+    T, W, FF = PROMPT, z["width"], z["ff"]
+    y, res = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+    g = torch.ones(W, dtype=bf, device=dev)
+    gf = torch.ones(W, device=dev)
+    ms_like = _time_kernel(lambda: K.residual_rmsnorm(y, g, 1e-6, res, bf), flush=flush)
+    by_bytes("stream_add_norm", _time_kernel(lambda: K.stream_add_norm(res, y, (gf, 1e-6), bf), flush=flush), T * W * (4 + 4 + 4 + 2),
+             like_bytes("residual_rmsnorm", ms_like, T * W * (4 + 4 + 4 + 2)))
+    gu = torch.randn(T, 2 * FF, device=dev)
+    ms_like = _time_kernel(lambda: K.act_mul(gu, "gelu_tanh", bf), flush=flush)
+    by_bytes("act_mul_clamp", _time_kernel(lambda: K.act_mul(gu, "swiglu_clamp", bf, limit=7.0, alpha=1.702), flush=flush), T * FF * (8 + 2),
+             like_bytes("act_mul_gelu", ms_like, T * FF * (8 + 2)))
+
+    # attention: what follows the q/k/v product, one prompt of 2,048 tokens, and a decode step of `batch` sequences behind 2,048 tokens
+    nh, nkv, hd = z["heads"], z["kv_heads"], z["dim"]
+    pages = PROMPT // 16
+    cache1 = torch.zeros(pages, 2, nkv, 16, hd, dtype=bf, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * torch.tensor([500000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64)[None, :]
+    cos, sin = torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+    proj_qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=dev)
+    ms_like = _time_kernel(lambda: K.rope_cache_write(proj_qkv, None, pos, cos, sin, pos, cache1, nh, nkv, hd, out_dtype=bf), flush=flush)
+    by_bytes("kv_prepare", _time_kernel(lambda: K.kv_prepare(proj_qkv, pos, cache1, nh, nkv, hd, hd, 1e-6, bf), flush=flush),
+             T * (nh + 2 * nkv) * hd * 6, like_bytes("rope_cache_write", ms_like, T * (nh + 2 * nkv) * hd * 6))
+    r1, r2 = torch.full((nh,), 0.5, device=dev), torch.full((nh,), 0.3, device=dev)
+    talk = (torch.eye(nh, device=dev) + 0.1 * torch.randn(nh, nh, device=dev)).contiguous()
+
+    def attention_case(q_len, ctx, seqs):
+        pages = seqs * (ctx // 16)
+        cache = torch.randn(pages, 2, nkv, 16, hd, device=dev).to(bf)
+        tables = torch.arange(pages, dtype=torch.int32, device=dev).view(seqs, ctx // 16)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        meta = AttentionMeta(tables, cu, torch.full((seqs,), ctx, dtype=torch.int32, device=dev),
+                             torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len), None, seqs, q_len, ctx, 16,
+                             seqs if q_len == 1 else 0)
+        q = torch.randn(seqs * q_len, nh * hd, device=dev).to(bf)
+        positions = (torch.arange(q_len, dtype=torch.int32, device=dev) + (ctx - q_len)).repeat(seqs)
+        return q, cache, meta, positions
+
+    q, cache, meta, positions = attention_case(PROMPT, PROMPT, 1)
+    flops = 4.0 * nh * hd * PROMPT * PROMPT / 2
+    ms_like = _time_kernel(lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None), flush=flush)
+    ms = _time_kernel(lambda: K.talking_attention(q, cache, meta, positions, nh, nkv, hd, hd, hd ** -0.5, r1, r2, talk, TIBEPEL_CHUNK), iters=3, flush=flush)
+    out["kernels"]["talking_attention_prefill"] = {
+        "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_bf16": round(flops / (ms / 1e3) / peak, 3),
+        "like": {"kernel": "attention_prefill", "ms": round(ms_like, 4), "frac_bf16": round(flops / (ms_like / 1e3) / peak, 3)}}
+    q, cache, meta, positions = attention_case(1, PROMPT, batch)
+    nbytes = batch * PROMPT * 2 * nkv * hd * 2
+    ms_like = _time_kernel(lambda: K.paged_attention(q, cache, meta, nh, nkv, hd, hd ** -0.5, None), flush=flush)
+    by_bytes("talking_attention_decode",
+             _time_kernel(lambda: K.talking_attention(q, cache, meta, positions, nh, nkv, hd, hd, hd ** -0.5, r1, r2, talk, TIBEPEL_CHUNK), flush=flush),
+             nbytes, like_bytes("attention_decode", ms_like, nbytes))
+
+    # the recurrences: a 2,048-token prompt, and a decode step of `batch` sequences; beside the state-space scan of the Tufirax path
+    H, P, N, G = z["m_heads"], z["m_vdim"], z["m_state"], z["groups"]
+    m_inner, ch = H * P, H * P + 2 * G * N
+    inner, N1, R = z["inner"], z["state"], z["dt_rank"]
+    rh, rk, rd, rv = z["r_heads"], z["r_kv"], z["r_dim"], z["r_vdim"]
+    for label, q_len, seqs in (("prefill", PROMPT, 1), ("decode", 1, batch)):
+        rows = q_len * seqs
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        # the like kernel: the scan with one decay per head
+        proj = torch.randn(rows, 2 * m_inner + 2 * G * N + H, device=dev)
+        xbc = torch.randn(rows, ch, device=dev).to(bf)
+        state = torch.zeros(seqs, H * N * P, device=dev)
+        zeros_h, ones_h = torch.zeros(H, device=dev), torch.ones(H, device=dev)
+        ms_like = _time_kernel(lambda: K.ssm_scan(xbc, proj, m_inner + ch, zeros_h, zeros_h, ones_h, cu, slots, state, H, P, N, G), flush=flush)
+        like_b = rows * (ch * 2 + m_inner * 4) + seqs * H * N * P * 8
+        like = dict(like_bytes("ssm_scan", ms_like, like_b), gflops=round(rows * H * P * N * 5 / ms_like / 1e6, 1))
+        # mamba1: one state row per channel
+        u = torch.randn(rows, inner, device=dev).to(bf)
+        dt_raw, bc, zz = torch.randn(rows, inner, device=dev), torch.randn(rows, R + 2 * N1, device=dev), torch.randn(rows, 2 * inner, device=dev)
+        A, dtb, dsk = -torch.rand(inner, N1, device=dev), torch.zeros(inner, device=dev), torch.ones(inner, device=dev)
+        st1 = torch.zeros(seqs, inner * N1, device=dev)
+        ms = _time_kernel(lambda: K.selective_scan(u, dt_raw, dtb, A, bc, R, R + N1, dsk, zz, inner, cu, slots, st1, bf), flush=flush)
+        by_bytes(f"selective_scan_{label}", ms, rows * (inner * (2 + 4 + 4 + 2) + 2 * N1 * 4) + seqs * inner * N1 * 8 + inner * N1 * 4, like)
+        out["kernels"][f"selective_scan_{label}"]["gflops"] = round(rows * inner * N1 * 6 / ms / 1e6, 1)
+        # the gated delta rule
+        qkv = torch.randn(rows, 2 * rk * rd + rh * rv, device=dev).to(bf)
+        pr = torch.randn(rows, 2 * rh, device=dev)
+        st2 = torch.zeros(seqs, rh * rd * rv, device=dev)
+        al, db = torch.zeros(rh, device=dev), torch.zeros(rh, device=dev)
+        ms = _time_kernel(lambda: K.delta_rule(qkv, pr, 0, rh, al, db, cu, slots, st2, rh, rk, rd, rv, 1e-6), flush=flush)
+        by_bytes(f"delta_rule_{label}", ms, rows * ((2 * rk * rd + rh * rv) * 2 + rh * rv * 4 + 2 * rh * 4) + seqs * rh * rd * rv * 8, like)
+        out["kernels"][f"delta_rule_{label}"]["gflops"] = round(rows * rh * rd * rv * 6 / ms / 1e6, 1)
+        o = torch.randn(rows, rh * rv, device=dev)
+        gate = torch.randn(rows, rh * rv, device=dev)
+        gw = torch.ones(rv, dtype=bf, device=dev)
+        yv, gproj, nw = torch.randn(rows, m_inner, device=dev), torch.randn(rows, m_inner, device=dev), torch.ones(m_inner, dtype=bf, device=dev)
+        ms_like = _time_kernel(lambda: K.gated_group_rmsnorm(yv, gproj, nw, 1e-6, G, bf), flush=flush)
+        by_bytes(f"head_norm_gate_{label}", _time_kernel(lambda: K.head_norm_gate(o, gw, 1e-6, gate, 0, rh, rv, bf), flush=flush),
+                 rows * rh * rv * (4 + 4 + 2), like_bytes("gated_group_rmsnorm", ms_like, rows * m_inner * (4 + 4 + 2)))
+    K.raise_on_abort()
+    print(json.dumps(out))
+
+
 def run_serve(args):
     print(json.dumps(serve_workload(args.shape, args.layers, args.requests, args.output_len, args.budget, args.eager)))
 
@@ -800,10 +1010,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes of the model")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax", "vipelix"],
-                    help="decode: the benchmark's one JSON line; serve: continuous batching of uneven prompts; tufirax, vipelix: that "
-                         "design at real layer sizes beside the Llama decoder of equal size, and its kernels alone")
-    ap.add_argument("--sizes", default="", help="tufirax, vipelix: which sizes to run, with commas (default: all)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax", "vipelix", "tibepel"],
+                    help="decode: the benchmark's one JSON line; serve: continuous batching of uneven prompts; tufirax, vipelix, tibepel: "
+                         "that design at real layer sizes beside the closest decoder of equal size, and its kernels alone")
+    ap.add_argument("--sizes", default="", help="tufirax, vipelix, tibepel: which sizes to run, with commas (default: all)")
     ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")
     ap.add_argument("--output-len", type=int, default=256, help="serve: tokens generated per request")
     ap.add_argument("--budget", type=int, default=2048, help="serve: tokens per step")
@@ -825,6 +1035,8 @@ def main():
         run_tufirax(args)
     elif args.workload == "vipelix":
         run_vipelix(args)
+    elif args.workload == "tibepel":
+        run_tibepel(args)
     elif args.workload == "serve":
         run_serve(args)
     else:

@@ -335,7 +335,7 @@ _cache = {}
 def _reference(which):
     if which not in _cache:
         from rvllm_b200 import load_config
-        folder = X.write_folder({"a": X.small_a, "b": X.small_b}[which](), seed=5, edit=X.lively)
+        folder = X.write_folder({"a": X.small_a, "b": X.small_b}[which](), seed=6, edit=X.lively)
         vocab = load_config(folder).vocab_size
         reqs = random_requests(vocab, LENGTHS[which], seed=4)
         _cache[which] = (folder, vocab, reqs, X.plain_logits(folder, reqs), X.plain_logits(folder, reqs, rounded=True))
