@@ -537,12 +537,16 @@ RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void
 // The older form of the selective scan: every channel c has its own decays A[c, :] and its own step size,
 //     S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n ,   y_c = sum_n S[c, n] C_n + D_c u_c ,   out_c = y_c silu(z_c)
 // with dt_c = softplus(raw_c + bias_c); B and C are shared by all channels of a token.  S lives as [inner][N] at
-// offset 0 of the request's state row.  A channel is served by `parts` neighbouring lanes with up to SCAN1_NS states
+// offset 0 of the request's state row.  A channel is served by `parts` neighbouring lanes with up to NS states
 // each (partial sums meet by shuffles), a block by 128 threads; grid (channel blocks, sequences).  The tokens' B
 // and C wait in shared memory in chunks of SCAN1_CHUNK tokens.
-#define SCAN1_NS 16
 #define SCAN1_CHUNK 16
 
+// Shared memory (floats): B | C of the chunk [SCAN1_CHUNK][2 N], then per token and channel of the block the step size
+// [SCAN1_CHUNK][per_block] and the input [SCAN1_CHUNK][per_block] (which the walk overwrites with y).  Softplus, the loads
+// of a chunk and the gate y silu(z) with its store are done by all threads side by side; only the recurrence itself
+// walks token by token, out of shared memory.
+template <int NS>
 __global__ void __launch_bounds__(128)
 selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
                        const float* __restrict__ A, const float* __restrict__ bc, int bc_stride, int b_col0, int c_col0,
@@ -557,19 +561,23 @@ selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __r
     if (slot < 0) return;
     const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
     const int per_block = blockDim.x / parts;
-    const int c = blockIdx.x * per_block + threadIdx.x / parts;
+    float* sDt = sBC + SCAN1_CHUNK * 2 * N;            // [SCAN1_CHUNK][per_block]
+    float* sU = sDt + SCAN1_CHUNK * per_block;         // [SCAN1_CHUNK][per_block]
+    const int c_first = blockIdx.x * per_block;
+    const int cl = threadIdx.x / parts;
+    const int c = c_first + cl;
     const int part = threadIdx.x % parts;
     const bool live = c < inner;
-    const int n0 = part * SCAN1_NS;
-    float S[SCAN1_NS], a[SCAN1_NS];
+    const int n0 = part * NS;
+    float S[NS], a[NS];
     float* srow = state + (size_t)slot * state_stride + (size_t)c * N;
 #pragma unroll
-    for (int i = 0; i < SCAN1_NS; ++i) {
+    for (int i = 0; i < NS; ++i) {
         const bool ok = live && n0 + i < N;
         S[i] = ok ? srow[n0 + i] : 0.f;
         a[i] = ok ? A[(size_t)c * N + n0 + i] : 0.f;
     }
-    const float bias = live ? dt_bias[c] : 0.f, dsk = live ? d_skip[c] : 0.f;
+    const float dsk = live ? d_skip[c] : 0.f;
     for (int t0 = 0; t0 < n_tok; t0 += SCAN1_CHUNK) {
         const int nt = min(SCAN1_CHUNK, n_tok - t0);
         __syncthreads();
@@ -577,34 +585,49 @@ selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __r
             const int tt = i / (2 * N), j = i - tt * 2 * N;
             sBC[i] = bc[(size_t)(start + t0 + tt) * bc_stride + (j < N ? b_col0 + j : c_col0 + j - N)];
         }
+        for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
+            const int tt = i / per_block, cc = c_first + (i - tt * per_block);
+            float dt = 0.f, uv = 0.f;
+            if (cc < inner) {
+                const size_t row = (size_t)(start + t0 + tt);
+                const float raw = dt_raw[row * inner + cc] + dt_bias[cc];
+                dt = raw > 20.f ? raw : log1pf(expf(raw));
+                uv = rv_load_any(u, u_dtype, row * inner + cc);
+            }
+            sDt[i] = dt;
+            sU[i] = uv;
+        }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {                   // (threads beyond the last channel walk along: the shuffles need every lane)
-            const size_t row = (size_t)(start + t0 + tt);
-            const float raw = (live ? dt_raw[row * inner + c] : 0.f) + bias;
-            const float dt = raw > 20.f ? raw : log1pf(expf(raw));
-            const float uv = live ? rv_load_any(u, u_dtype, row * inner + c) : 0.f;
+            const float dt = sDt[tt * per_block + cl];
+            const float uv = sU[tt * per_block + cl];
             const float du = dt * uv;
             const float* B = sBC + tt * 2 * N + n0;
             const float* C = B + N;
             float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < SCAN1_NS; ++i) {
+            for (int i = 0; i < NS; ++i) {
                 if (n0 + i < N) {
                     S[i] = fmaf(expf(dt * a[i]), S[i], du * B[i]);
                     acc = fmaf(S[i], C[i], acc);
                 }
             }
             for (int o = 1; o < parts; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (part == 0 && live) {
-                const float y = fmaf(dsk, uv, acc);
-                const float zv = rv_load_any(z, z_dtype, row * z_stride + z_col0 + c);
-                rv_store_any(out, out_dtype, row * inner + c, y * (zv / (1.0f + expf(-zv))));
+            if (part == 0) sU[tt * per_block + cl] = fmaf(dsk, uv, acc);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
+            const int tt = i / per_block, cc = c_first + (i - tt * per_block);
+            if (cc < inner) {
+                const size_t row = (size_t)(start + t0 + tt);
+                const float zv = rv_load_any(z, z_dtype, row * z_stride + z_col0 + cc);
+                rv_store_any(out, out_dtype, row * inner + cc, sU[i] * (zv / (1.0f + expf(-zv))));
             }
         }
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < SCAN1_NS; ++i)
+        for (int i = 0; i < NS; ++i)
             if (n0 + i < N) srow[n0 + i] = S[i];
     }
 }
@@ -613,19 +636,24 @@ RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw
                                  const float* bc, int bc_stride, int b_col0, int c_col0, const float* d_skip, const void* z,
                                  int z_dtype, int z_stride, int z_col0, const int* cu_seqlens, const int* state_slots, float* state,
                                  long long state_stride, void* out, int out_dtype, int n_seqs, int inner, int N, cudaStream_t stream) {
-    if (n_seqs < 0 || inner <= 0 || N <= 0 || N > 32 * SCAN1_NS || n_seqs > 65535) return RV_ERR_BAD_SIZE;
+    if (n_seqs < 0 || inner <= 0 || N <= 0 || N > 32 * 16 || n_seqs > 65535) return RV_ERR_BAD_SIZE;
     if (b_col0 < 0 || c_col0 < 0 || b_col0 + N > bc_stride || c_col0 + N > bc_stride || z_col0 < 0 || z_col0 + inner > z_stride ||
         state_stride < (long long)inner * N)
         return RV_ERR_BAD_SIZE;
     if ((u_dtype | z_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
     if (n_seqs == 0) return RV_OK;
+    // four states per lane where a warp's lanes can hold a channel's row so (neighbouring lanes then read neighbouring
+    // 16 bytes of the state, and four times as many threads walk the tokens); sixteen per lane for longer rows
+    const int ns = N <= 32 * 4 ? 4 : 16;
     int parts = 1;
-    while (parts * SCAN1_NS < N) parts <<= 1;          // a power of two of at most 32 lanes of one warp
+    while (parts * ns < N) parts <<= 1;                // a power of two of at most 32 lanes of one warp
     const int per_block = 128 / parts;
-    RV_LAUNCH_ST = rv_launch(selective_scan1_kernel, dim3((inner + per_block - 1) / per_block, n_seqs), dim3(128),
-                             (size_t)SCAN1_CHUNK * 2 * N * sizeof(float), stream, u, u_dtype, dt_raw, dt_bias, A, bc, bc_stride,
-                             b_col0, c_col0, d_skip, z, z_dtype, z_stride, z_col0, cu_seqlens, state_slots, state,
-                             (size_t)state_stride, out, out_dtype, inner, N, parts);
+    const size_t smem = (size_t)SCAN1_CHUNK * (2 * N + 2 * per_block) * sizeof(float);
+    if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
+    auto kernel = ns == 4 ? selective_scan1_kernel<4> : selective_scan1_kernel<16>;
+    RV_LAUNCH_ST = rv_launch(kernel, dim3((inner + per_block - 1) / per_block, n_seqs), dim3(128), smem, stream, u, u_dtype, dt_raw,
+                             dt_bias, A, bc, bc_stride, b_col0, c_col0, d_skip, z, z_dtype, z_stride, z_col0, cu_seqlens, state_slots,
+                             state, (size_t)state_stride, out, out_dtype, inner, N, parts);
     return rv_launch_status();
 }
 
@@ -661,6 +689,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
     float* sK = sQ + DR_CHUNK * row_floats;
     float* sG = sK + DR_CHUNK * row_floats;                // [DR_CHUNK]
     float* sBeta = sG + DR_CHUNK;
+    float* sV = sBeta + DR_CHUNK;                          // [DR_CHUNK][128 / parts]: the chunk's values of the block's columns
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per_block = 128 / parts;
     const int col = blockIdx.x * per_block + tid / parts;
@@ -700,6 +729,10 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
                 sK[at] *= rk;
             }
         }
+        for (int i = tid; i < nt * per_block; i += 128) {
+            const int tt = i / per_block, cc = blockIdx.x * per_block + (i - tt * per_block);
+            sV[i] = cc < vd ? rv_load_any(qkv, qkv_dtype, (size_t)(start + t0 + tt) * qkv_stride + 2 * qk + (size_t)h * vd + cc) : 0.f;
+        }
         if (tid < nt) {
             const size_t row = (size_t)(start + t0 + tid) * proj_stride;
             const float b = proj[row + b_col0 + h];
@@ -713,28 +746,30 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
             const size_t trow = (size_t)(start + t0 + tt);
             const float4* K4 = reinterpret_cast<const float4*>(sK + tt * row_floats + part * DR_PAD);
             const float4* Q4 = reinterpret_cast<const float4*>(sQ + tt * row_floats + part * DR_PAD);
-            const float vv = live ? rv_load_any(qkv, qkv_dtype, trow * qkv_stride + 2 * qk + (size_t)h * vd + col) : 0.f;
+            const float vv = sV[tt * per_block + tid / parts];
             float kreg[DR_NS];
-            float acc = 0.f;
+            float ac[4] = {0.f, 0.f, 0.f, 0.f};                // four sums side by side: the chain of a column is a quarter as long
 #pragma unroll
             for (int i = 0; i < DR_NS / 4; ++i) {
                 const float4 k4 = K4[i];
                 kreg[4 * i] = k4.x; kreg[4 * i + 1] = k4.y; kreg[4 * i + 2] = k4.z; kreg[4 * i + 3] = k4.w;
-                acc = fmaf(S[4 * i], k4.x, acc); acc = fmaf(S[4 * i + 1], k4.y, acc);
-                acc = fmaf(S[4 * i + 2], k4.z, acc); acc = fmaf(S[4 * i + 3], k4.w, acc);
+                ac[0] = fmaf(S[4 * i], k4.x, ac[0]); ac[1] = fmaf(S[4 * i + 1], k4.y, ac[1]);
+                ac[2] = fmaf(S[4 * i + 2], k4.z, ac[2]); ac[3] = fmaf(S[4 * i + 3], k4.w, ac[3]);
             }
+            float acc = (ac[0] + ac[1]) + (ac[2] + ac[3]);
             for (int o = 1; o < parts; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             const float g = sG[tt];
             const float u = sBeta[tt] * (vv - g * acc);
-            float ov = 0.f;
+            float ov4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < DR_NS / 4; ++i) {
                 const float4 q4 = Q4[i];
-                S[4 * i] = fmaf(g, S[4 * i], kreg[4 * i] * u);             ov = fmaf(S[4 * i], q4.x, ov);
-                S[4 * i + 1] = fmaf(g, S[4 * i + 1], kreg[4 * i + 1] * u); ov = fmaf(S[4 * i + 1], q4.y, ov);
-                S[4 * i + 2] = fmaf(g, S[4 * i + 2], kreg[4 * i + 2] * u); ov = fmaf(S[4 * i + 2], q4.z, ov);
-                S[4 * i + 3] = fmaf(g, S[4 * i + 3], kreg[4 * i + 3] * u); ov = fmaf(S[4 * i + 3], q4.w, ov);
+                S[4 * i] = fmaf(g, S[4 * i], kreg[4 * i] * u);             ov4[0] = fmaf(S[4 * i], q4.x, ov4[0]);
+                S[4 * i + 1] = fmaf(g, S[4 * i + 1], kreg[4 * i + 1] * u); ov4[1] = fmaf(S[4 * i + 1], q4.y, ov4[1]);
+                S[4 * i + 2] = fmaf(g, S[4 * i + 2], kreg[4 * i + 2] * u); ov4[2] = fmaf(S[4 * i + 2], q4.z, ov4[2]);
+                S[4 * i + 3] = fmaf(g, S[4 * i + 3], kreg[4 * i + 3] * u); ov4[3] = fmaf(S[4 * i + 3], q4.w, ov4[3]);
             }
+            float ov = (ov4[0] + ov4[1]) + (ov4[2] + ov4[3]);
             for (int o = 1; o < parts; o <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
             if (part == 0 && live) out[trow * heads * vd + (size_t)h * vd + col] = ov;
         }
@@ -763,7 +798,7 @@ RV_EXPORT int rv_delta_rule(const void* qkv, int qkv_dtype, int qkv_stride, cons
     int parts = 1;
     while (parts * DR_NS < d) parts <<= 1;             // a power of two of at most 32 lanes of one warp
     const int per_block = 128 / parts;
-    const size_t smem = sizeof(float) * (2 * (size_t)DR_CHUNK * parts * DR_PAD + 2 * DR_CHUNK);
+    const size_t smem = sizeof(float) * (2 * (size_t)DR_CHUNK * parts * DR_PAD + 2 * DR_CHUNK + (size_t)DR_CHUNK * per_block);
     if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
     RV_LAUNCH_ST = rv_launch(delta_rule_kernel, dim3((vd + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, qkv,
                              qkv_dtype, qkv_stride, proj, proj_stride, b_col0, a_col0, a_log, dt_bias, cu_seqlens, state_slots, state,

@@ -270,3 +270,247 @@ RV_EXPORT int rv_talking_attention(const void* q, const void* cache, const int* 
     TA_GO(3, __nv_bfloat16, false);
 #undef TA_GO
 }
+
+// ------------------------------------------------------------------ few tokens, many keys: the keys split over CTAs
+// A step of single tokens gives the kernel above one CTA per sequence, which walks all its keys alone.  Here a
+// token's visible keys are cut into `nsplit` ranges of `span` keys, and three launches do the work:
+//   scores   CTA (token, range): every head's scores of the range into `S` [tokens][nh][nsplit * span] (float), and the
+//            range's maximum and sum of exponentials per head into `stats` [tokens][nsplit][nh][2]
+//   apply    CTA (token, range): joins the token's statistics, turns the range's scores into normalised weights, mixes
+//            the heads and sums the range's values into `part` [tokens][nsplit][nh * vd] (float)
+//   join     CTA per token: adds the parts in the order of the ranges
+// The weights are linear in the values once every head's maximum and denominator are known, so the parts only add.
+struct TaWhere {
+    int ctx, pos, lo, k0, k1, nvalid;
+    const int* table;
+};
+
+__device__ __forceinline__ TaWhere ta_where(const int* block_tables, const int* cu_seqlens, const int* ctx_lens, const int* token_seq, int t,
+                                            int sp, int span, int chunk, int max_blocks) {
+    TaWhere w;
+    const int seq = token_seq[t];
+    w.ctx = seq >= 0 ? ctx_lens[seq] : 0;
+    w.pos = w.lo = w.k0 = w.k1 = w.nvalid = 0;
+    w.table = nullptr;
+    if (w.ctx <= 0) return w;
+    const int q_start = cu_seqlens[seq];
+    const int q_len = cu_seqlens[seq + 1] - q_start;
+    w.pos = w.ctx - q_len + (t - q_start);
+    w.lo = chunk > 0 ? (w.pos / chunk) * chunk : 0;
+    w.k0 = w.lo + sp * span;
+    w.k1 = min(w.k0 + span, w.pos + 1);
+    w.nvalid = (w.pos - w.lo) / span + 1;
+    w.table = block_tables + (size_t)seq * max_blocks;
+    return w;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(TA_THREADS)
+ta_split_scores_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_tables,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens, const int* __restrict__ token_seq,
+                       float* __restrict__ S, float* __restrict__ stats, int nh, int nkv, int hd, int vd, int page_size, int max_blocks,
+                       float scale, const float* __restrict__ r1, const float* __restrict__ r2, int chunk, int span, int nsplit) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ __align__(16) unsigned char ta_smem[];
+    float* qs = reinterpret_cast<float*>(ta_smem);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int t = blockIdx.x, sp = blockIdx.y;
+    const TaWhere w = ta_where(block_tables, cu_seqlens, ctx_lens, token_seq, t, sp, span, chunk, max_blocks);
+    if (w.ctx <= 0 || w.k0 > w.pos) return;
+    for (int i = tid; i < nh * hd; i += TA_THREADS) qs[i] = rv_to_float(q[(size_t)t * nh * hd + i]);
+    __syncthreads();
+    const int rep = nh / nkv;
+    const size_t page_elems = (size_t)nkv * page_size * (hd + vd);
+    const bool biased = r1 != nullptr;
+    const size_t stride = (size_t)nsplit * span;
+    for (int h = warp; h < nh; h += TA_WARPS) {
+        const float a1 = biased ? r1[h] : 0.f, a2 = biased ? r2[h] : 0.f;
+        float* row = S + ((size_t)t * nh + h) * stride;
+        float m = -INFINITY, l = 0.f;
+        for (int j = w.k0 + lane; j < w.k1; j += 32) {
+            const float s = ta_score<T, VEC>(cache, w.table, page_elems, page_size, hd, h / rep, j, w.pos, qs + (size_t)h * hd, scale, a1, a2, biased);
+            row[j - w.lo] = s;
+            const float m_new = fmaxf(m, s);
+            l = l * expf(m - m_new) + expf(s - m_new);
+            m = m_new;
+        }
+        const float M = rv_warp_max(m);
+        l = rv_warp_sum(m == -INFINITY ? 0.f : l * expf(m - M));
+        if (lane == 0) {
+            float* st = stats + (((size_t)t * nsplit + sp) * nh + h) * 2;
+            st[0] = M;
+            st[1] = l;
+        }
+    }
+}
+
+// Shared memory: TA_TILE 64-bit offsets | O [nh * vd] | P [nh][TA_TILE] | P' [nh][TA_TILE] | talk [nh * nh] | m [nh] | 1/l [nh].
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(TA_THREADS)
+ta_split_apply_kernel(const T* __restrict__ cache, const int* __restrict__ block_tables, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ ctx_lens, const int* __restrict__ token_seq, const float* __restrict__ S,
+                      const float* __restrict__ stats, const float* __restrict__ talk, float* __restrict__ part, int nh, int nkv, int hd,
+                      int vd, int page_size, int max_blocks, int chunk, int span, int nsplit) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    extern __shared__ __align__(16) unsigned char ta_smem[];
+    const int tid = threadIdx.x;
+    const int t = blockIdx.x, sp = blockIdx.y;
+    const TaWhere w = ta_where(block_tables, cu_seqlens, ctx_lens, token_seq, t, sp, span, chunk, max_blocks);
+    if (w.ctx <= 0 || w.k0 > w.pos) return;
+    size_t* vrow = reinterpret_cast<size_t*>(ta_smem);
+    float* Os = reinterpret_cast<float*>(ta_smem + TA_TILE * sizeof(size_t));
+    float* P = Os + (size_t)nh * vd;
+    float* PM = talk ? P + nh * TA_TILE : P;
+    float* talk_s = P + 2 * nh * TA_TILE;
+    float* ms = talk_s + nh * nh;
+    float* linv = ms + nh;
+    const int rep = nh / nkv;
+    const size_t page_elems = (size_t)nkv * page_size * (hd + vd);
+    const size_t v_off = (size_t)nkv * page_size * hd;
+    const size_t stride = (size_t)nsplit * span;
+
+    for (int h = tid; h < nh; h += TA_THREADS) {
+        const float* st = stats + ((size_t)t * nsplit * nh + h) * 2;
+        float M = -INFINITY;
+        for (int s = 0; s < w.nvalid; ++s) M = fmaxf(M, st[(size_t)s * nh * 2]);
+        float L = 0.f;
+        for (int s = 0; s < w.nvalid; ++s) L += st[(size_t)s * nh * 2 + 1] * expf(st[(size_t)s * nh * 2] - M);
+        ms[h] = M;
+        linv[h] = 1.0f / L;
+    }
+    for (int i = tid; i < nh * vd; i += TA_THREADS) Os[i] = 0.f;
+    if (talk)
+        for (int i = tid; i < nh * nh; i += TA_THREADS) talk_s[i] = talk[i];
+    __syncthreads();
+
+    constexpr int EV = VEC ? 16 / (int)sizeof(T) : 1;      // value elements per thread and key
+    const int vblocks = vd / EV;
+    for (int j0 = w.k0; j0 < w.k1; j0 += TA_TILE) {
+        const int nk = min(TA_TILE, w.k1 - j0);
+        for (int i = tid; i < nh * TA_TILE; i += TA_THREADS) {
+            const int h = i / TA_TILE, jj = i - h * TA_TILE;
+            P[i] = jj < nk ? expf(S[((size_t)t * nh + h) * stride + (j0 + jj - w.lo)] - ms[h]) * linv[h] : 0.f;
+        }
+        if (tid < nk) {
+            const int j = j0 + tid;
+            vrow[tid] = (size_t)w.table[j / page_size] * page_elems + v_off + (size_t)(j % page_size) * vd;
+        }
+        __syncthreads();
+        if (talk) {
+            for (int i = tid; i < nh * TA_TILE; i += TA_THREADS) {
+                const int h = i / TA_TILE, jj = i - h * TA_TILE;
+                float a = 0.f;
+                for (int g = 0; g < nh; ++g) a = fmaf(talk_s[h * nh + g], P[g * TA_TILE + jj], a);
+                PM[i] = a;
+            }
+            __syncthreads();
+        }
+        for (int i = tid; i < nh * vblocks; i += TA_THREADS) {
+            const int h = i / vblocks, e = (i - h * vblocks) * EV;
+            const size_t head_off = (size_t)(h / rep) * page_size * vd + e;
+            const float* pw = PM + h * TA_TILE;
+            float acc[EV];
+#pragma unroll
+            for (int x = 0; x < EV; ++x) acc[x] = Os[h * vd + e + x];
+            for (int jj = 0; jj < nk; ++jj) {
+                const float p = pw[jj];
+                const T* vp = cache + vrow[jj] + head_off;
+                if constexpr (VEC && sizeof(T) == 2) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(vp);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const float2 f = __bfloat1622float2(h2[x]);
+                        acc[2 * x] = fmaf(p, f.x, acc[2 * x]);
+                        acc[2 * x + 1] = fmaf(p, f.y, acc[2 * x + 1]);
+                    }
+                } else if constexpr (VEC) {
+                    const float4 f = *reinterpret_cast<const float4*>(vp);
+                    acc[0] = fmaf(p, f.x, acc[0]); acc[1] = fmaf(p, f.y, acc[1]);
+                    acc[2] = fmaf(p, f.z, acc[2]); acc[3] = fmaf(p, f.w, acc[3]);
+                } else {
+                    acc[0] = fmaf(p, rv_to_float(vp[0]), acc[0]);
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < EV; ++x) Os[h * vd + e + x] = acc[x];
+        }
+        __syncthreads();
+    }
+    float* o = part + ((size_t)t * nsplit + sp) * nh * vd;
+    for (int i = tid; i < nh * vd; i += TA_THREADS) o[i] = Os[i];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(TA_THREADS)
+ta_split_join_kernel(const float* __restrict__ part, const int* __restrict__ cu_seqlens, const int* __restrict__ ctx_lens,
+                     const int* __restrict__ token_seq, T* __restrict__ out, int width, int chunk, int span, int nsplit) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const int t = blockIdx.x;
+    const TaWhere w = ta_where(nullptr, cu_seqlens, ctx_lens, token_seq, t, 0, span, chunk, 0);
+    for (int i = threadIdx.x; i < width; i += TA_THREADS) {
+        float a = 0.f;
+        for (int s = 0; s < w.nvalid; ++s) a += part[((size_t)t * nsplit + s) * width + i];
+        out[(size_t)t * width + i] = rv_from_float<T>(a);
+    }
+}
+
+static RvPerDevice g_ta_split_once[4];
+
+template <typename T, bool VEC>
+static int ta_split_launch(int which, const void* q, const void* cache, const int* block_tables, const int* cu_seqlens, const int* ctx_lens,
+                           const int* token_seq, void* out, float* S, float* stats, float* part, int n_tokens, int nh, int nkv, int hd,
+                           int vd, int page_size, int max_blocks, float scale, const float* r1, const float* r2, const float* talk, int chunk,
+                           int span, int nsplit, size_t smem, cudaStream_t stream) {
+    const int st = rv_configure_smem(g_ta_split_once[which], ta_split_apply_kernel<T, VEC>, 200 * 1024);
+    if (st != RV_OK) return st;
+    RV_LAUNCH_ST = rv_launch(ta_split_scores_kernel<T, VEC>, dim3(n_tokens, nsplit), dim3(TA_THREADS), sizeof(float) * (size_t)nh * hd, stream,
+                             (const T*)q, (const T*)cache, block_tables, cu_seqlens, ctx_lens, token_seq, S, stats, nh, nkv, hd, vd, page_size,
+                             max_blocks, scale, r1, r2, chunk, span, nsplit);
+    if (rv_launch_status() != RV_OK) return rv_launch_status();
+    RV_LAUNCH_ST = rv_launch(ta_split_apply_kernel<T, VEC>, dim3(n_tokens, nsplit), dim3(TA_THREADS), smem, stream, (const T*)cache,
+                             block_tables, cu_seqlens, ctx_lens, token_seq, (const float*)S, (const float*)stats, talk, part, nh, nkv, hd, vd,
+                             page_size, max_blocks, chunk, span, nsplit);
+    if (rv_launch_status() != RV_OK) return rv_launch_status();
+    RV_LAUNCH_ST = rv_launch(ta_split_join_kernel<T>, dim3(n_tokens), dim3(TA_THREADS), 0, stream, (const float*)part, cu_seqlens, ctx_lens,
+                             token_seq, (T*)out, nh * vd, chunk, span, nsplit);
+    return rv_launch_status();
+}
+
+// Floats of scratch that rv_talking_attention_split needs behind `scratch`: S, then stats, then the parts.
+RV_EXPORT long long rv_talking_attention_split_floats(int n_tokens, int nh, int vd, int span, int nsplit) {
+    return (long long)n_tokens * nh * nsplit * span + (long long)n_tokens * nsplit * nh * 2 + (long long)n_tokens * nsplit * nh * vd;
+}
+
+// As rv_talking_attention, the visible keys of every token cut into `nsplit` ranges of `span` keys (nsplit * span covers
+// the longest visible run of the step); `scratch` holds rv_talking_attention_split_floats floats.
+RV_EXPORT int rv_talking_attention_split(const void* q, const void* cache, const int* block_tables, const int* cu_seqlens,
+                                         const int* ctx_lens, const int* token_seq, void* out, float* scratch, int n_tokens, int nh, int nkv,
+                                         int hd, int vd, int page_size, int max_blocks, float scale, const float* r1, const float* r2,
+                                         const float* talk, int chunk, int span, int nsplit, int dtype, cudaStream_t stream) {
+    if (n_tokens < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || vd <= 0 || page_size <= 0 || max_blocks <= 0 || span <= 0 || nsplit <= 0)
+        return RV_ERR_BAD_SIZE;
+    if ((r1 == nullptr) != (r2 == nullptr)) return RV_ERR_BAD_SIZE;
+    if (dtype & ~1) return RV_ERR_BAD_DTYPE;
+    const size_t smem = TA_TILE * sizeof(size_t) +
+                        sizeof(float) * ((size_t)nh * vd + 2 * (size_t)nh * TA_TILE + (size_t)nh * nh + 2 * (size_t)nh);
+    if (smem > 200 * 1024 || sizeof(float) * (size_t)nh * hd > 48 * 1024) return RV_ERR_UNSUPPORTED;
+    if (n_tokens == 0) return RV_OK;
+    float* S = scratch;
+    float* stats = S + (size_t)n_tokens * nh * nsplit * span;
+    float* part = stats + (size_t)n_tokens * nsplit * nh * 2;
+    const int el = dtype == RV_DTYPE_F32 ? 4 : 2;
+    const bool vec = (hd * el) % 16 == 0 && (vd * el) % 16 == 0 && ((uintptr_t)cache % 16) == 0;
+#define TA_GO(W, T, V) return ta_split_launch<T, V>(W, q, cache, block_tables, cu_seqlens, ctx_lens, token_seq, out, S, stats, part, n_tokens, \
+                                                    nh, nkv, hd, vd, page_size, max_blocks, scale, r1, r2, talk, chunk, span, nsplit, smem, stream)
+    if (dtype == RV_DTYPE_F32) {
+        if (vec) TA_GO(0, float, true);
+        TA_GO(1, float, false);
+    }
+    if (vec) TA_GO(2, __nv_bfloat16, true);
+    TA_GO(3, __nv_bfloat16, false);
+#undef TA_GO
+}

@@ -77,6 +77,10 @@ class CudaKernels:
     PREFILL_SPLIT_K = True             # ... or, where 2 or 4 CTAs per tile still fit the SMs, with K cut over a cluster of CTAs per tile
     NARROW_TILES = True                # ... with tiles of 128 columns where those of 256 would occupy at most half of the SMs
     PAIR_GEMM = True                   # the tcgen05 GEMM runs on pairs of CTAs (cta_group::2) where the rows fill its 256-row tiles
+    TALKING_MMA = True                 # attention with mixed head weights: bfloat16 prompt portions go to the tensor-core kernel when it fits
+    TALKING_SPLIT = True               # attention with mixed head weights: few tokens behind many keys go to the split-key kernels
+    TALKING_SPLIT_MAX_TOKENS = 64      # ... up to this many tokens in the step
+    TALKING_SPLIT_SPAN = 64            # ... in ranges of a multiple of this many keys
     TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
@@ -1243,6 +1247,33 @@ class CudaKernels:
                 if p.numel() != n:
                     raise KernelError(f"talking_attention: {name} has {p.numel()} entries, expected {n}")
         out = torch.empty((T, num_heads * value_dim), dtype=q.dtype, device=q.device)
+        visible = min(meta.max_ctx_len, chunk) if chunk else meta.max_ctx_len
+        if self.TALKING_SPLIT and 0 < T <= self.TALKING_SPLIT_MAX_TOKENS and visible > self.TALKING_SPLIT_SPAN \
+                and num_heads * head_dim * 4 <= 48 * 1024:
+            # few tokens behind many keys: the keys of a token are cut over CTAs (at most 64 ranges)
+            span = self.TALKING_SPLIT_SPAN * ((visible + 64 * self.TALKING_SPLIT_SPAN - 1) // (64 * self.TALKING_SPLIT_SPAN))
+            nsplit = (visible + span - 1) // span
+            lib = self._lib("talking_attention.cu")
+            lib.rv_talking_attention_split_floats.restype = ctypes.c_longlong
+            n = lib.rv_talking_attention_split_floats(c_int(T), c_int(num_heads), c_int(value_dim), c_int(span), c_int(nsplit))
+            scratch = torch.empty((n,), dtype=torch.float32, device=q.device)
+            st = lib.rv_talking_attention_split(
+                _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(meta.token_seq),
+                _ptr(out), _ptr(scratch), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim), c_int(ps),
+                c_int(meta.max_blocks), c_float(scale), _ptr(r1), _ptr(r2), _ptr(talk), c_int(chunk or 0), c_int(span), c_int(nsplit),
+                c_int(self._dt(q, "q")), self._stream())
+            _check("talking_attention_split", st)
+            return out
+        if self.TALKING_MMA and q.dtype == torch.bfloat16 and T > 0:
+            lib = self._lib("talking_attention_mma.cu")
+            if lib.rv_talking_attention_mma_fits(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim)):
+                st = lib.rv_talking_attention_mma(
+                    _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(out),
+                    c_int(meta.num_seqs), c_int(meta.max_q_len), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim),
+                    c_int(ps), c_int(meta.max_blocks), c_float(scale), _ptr(r1), _ptr(r2), _ptr(talk), c_int(chunk or 0), self._stream())
+                if st != -4:            # (-4: the tiles of these sizes do not fit the shared memory; the plain kernel takes them)
+                    _check("talking_attention_mma", st)
+                    return out
         st = self._lib("talking_attention.cu").rv_talking_attention(
             _ptr(q), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens), _ptr(meta.token_seq),
             _ptr(out), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim), c_int(ps),

@@ -277,6 +277,57 @@ def test_mixed_head_attention_over_pages(K, dtype, H, G, d, vd, chunk, page):
             at += n
 
 
+@pytest.mark.parametrize("H,G,d,vd,chunk,page", [(8, 2, 64, 64, 40, 16), (16, 4, 128, 64, 133, 32), (4, 4, 32, 128, None, 8), (16, 1, 16, 16, 64, 16),
+                                                 (8, 8, 48, 96, 97, 16), (2, 1, 128, 128, 31, 8), (12, 6, 64, 32, 70, 16)])
+@pytest.mark.parametrize("path", ["tensor", "split", "plain"])
+def test_every_build_of_the_mixed_head_attention_gives_the_plain_result(K, H, G, d, vd, chunk, page, path):
+    """The tensor-core build (many tokens), the split-key build (few tokens behind many keys) and the plain kernel against
+    the slow implementation: portions that start and end inside tiles, chunks and pages, single tokens among them, head
+    groups of 1 to 16, key and value widths that differ."""
+    dtype = torch.bfloat16
+    ctx, q_lens = ((300, 171, 1, 260, 64), (150, 37, 1, 259, 2)) if path != "split" else ((300, 171, 1, 64), (3, 1, 1, 20))
+    ks = [rnd(c, G, d, seed=180 + i).to(dtype).double() for i, c in enumerate(ctx)]
+    vs = [rnd(c, G, vd, seed=190 + i).to(dtype).double() for i, c in enumerate(ctx)]
+    qs = [rnd(n, H, d, seed=200 + i).to(dtype).double() for i, n in enumerate(q_lens)]
+    r1, r2 = torch.rand(H, generator=torch.Generator().manual_seed(1), dtype=F64) * 1.5, torch.rand(H, generator=torch.Generator().manual_seed(2), dtype=F64) + 0.1
+    talk = torch.eye(H, dtype=F64) + 0.4 * rnd(H, H, seed=3)
+    cache, meta, positions = flat_pages(ks, vs, q_lens, page, dtype, chunk)
+    q = torch.cat(qs).reshape(sum(q_lens), H * d).to(dtype).cuda()
+    old = K.TALKING_MMA, K.TALKING_SPLIT
+    K.TALKING_MMA, K.TALKING_SPLIT = path == "tensor", path == "split"
+    try:
+        for use_bias, use_talk in ((True, True), (False, False)):
+            got = K.talking_attention(q, cache, meta, positions, H, G, d, vd, 0.3, r1.float().cuda() if use_bias else None,
+                                      r2.float().cuda() if use_bias else None, talk.float().cuda() if use_talk else None, chunk)
+            at = 0
+            for i, n in enumerate(q_lens):
+                full_q = torch.zeros(ctx[i], H, d, dtype=F64)
+                full_q[ctx[i] - n:] = qs[i]
+                want = P.mixed_head_attention(full_q, ks[i], vs[i], 0.3, r1 if use_bias else torch.zeros(H, dtype=F64), r2,
+                                              talk if use_talk else torch.eye(H, dtype=F64), chunk or 10 ** 9)[ctx[i] - n:]
+                assert rel_err(got[at:at + n], want.reshape(n, -1)) < TOL[dtype], (i, use_bias, use_talk)
+                at += n
+    finally:
+        K.TALKING_MMA, K.TALKING_SPLIT = old
+
+
+def test_a_planted_key_reaches_the_tensor_core_build(K):
+    """As the planted key below, in a long portion: the key at the first position of the last query's chunk takes the whole
+    weight, one position lower it is not seen."""
+    H, G, d, vd, page, dtype, q_len = 8, 2, 64, 64, 16, torch.bfloat16, 200
+    for chunk, ctx in ((320, 600), (250, 499), (48, 300)):
+        start = ((ctx - 1) // chunk) * chunk
+        v = rnd(ctx, G, vd, seed=5).to(dtype).double()
+        for key in (start, start - 1, ctx - 1):
+            k, q = torch.zeros(ctx, G, d, dtype=F64), torch.zeros(q_len, H, d, dtype=F64)
+            k[key, :, 3], q[-1, :, 3] = 8.0, 8.0
+            cache, meta, positions = flat_pages([k], [v], [q_len], page, dtype, chunk, seed=key)
+            got = K.talking_attention(q.reshape(q_len, H * d).to(dtype).cuda(), cache, meta, positions, H, G, d, vd, 1.0, None, None, None, chunk)
+            for h in range(H):
+                want = v[key, h // 4] if key >= start else v[start:, h // 4].mean(0)
+                assert float((got[-1, h * vd:(h + 1) * vd].double().cpu() - want).abs().max()) < 2e-2, (chunk, key, h)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("q_len", [1, 7])
 def test_a_planted_key_at_the_edges_of_a_chunk(K, dtype, q_len):
