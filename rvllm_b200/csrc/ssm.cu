@@ -15,6 +15,13 @@
 __device__ __forceinline__ float rv_load_any(const void* p, int dtype, size_t i) {
     return dtype == RV_DTYPE_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
 }
+// The bits of an element, unconverted (a load whose result nothing touches yet does not hold the warp up), and their value.
+__device__ __forceinline__ uint32_t rv_load_raw(const void* p, int dtype, size_t i) {
+    return dtype == RV_DTYPE_F32 ? ((const uint32_t*)p)[i] : (uint32_t)((const unsigned short*)p)[i];
+}
+__device__ __forceinline__ float rv_raw_value(uint32_t raw, int dtype) {
+    return __uint_as_float(dtype == RV_DTYPE_F32 ? raw : raw << 16);
+}
 __device__ __forceinline__ void rv_store_any(void* p, int dtype, size_t i, float v) {
     if (dtype == RV_DTYPE_F32) ((float*)p)[i] = v;
     else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
@@ -541,12 +548,17 @@ RV_EXPORT int rv_ssm_scan(const void* xbc, int x_dtype, int channels, const void
 // each (partial sums meet by shuffles), a block by 128 threads; grid (channel blocks, sequences).  The tokens' B
 // and C wait in shared memory in chunks of SCAN1_CHUNK tokens.
 #define SCAN1_CHUNK 16
+#define SCAN1_PRE 4          // per thread: (token, channel) pairs of a chunk that the prefetch holds, 128 / parts <= 8 * SCAN1_PRE
+#define SCAN1_PRE_BC 8       // per thread: B | C entries of a chunk that the prefetch holds, 2 N <= 8 * SCAN1_PRE_BC
 
 // Shared memory (floats): B | C of the chunk [SCAN1_CHUNK][2 N], then per token and channel of the block the step size
 // [SCAN1_CHUNK][per_block] and the input [SCAN1_CHUNK][per_block] (which the walk overwrites with y).  Softplus, the loads
 // of a chunk and the gate y silu(z) with its store are done by all threads side by side; only the recurrence itself
-// walks token by token, out of shared memory.
-template <int NS>
+// walks token by token, out of shared memory, four tokens at a time: their decays and inputs are worked out first (they
+// do not depend on the state), so that the chain from token to token is one multiply-add per state; the last one to
+// three tokens of a sequence go one by one.
+// PRE: the raw inputs of the next chunk are loaded into registers, unconverted, before the current one is walked.
+template <int NS, bool PRE>
 __global__ void __launch_bounds__(128)
 selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
                        const float* __restrict__ A, const float* __restrict__ bc, int bc_stride, int b_col0, int c_col0,
@@ -578,27 +590,109 @@ selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __r
         a[i] = ok ? A[(size_t)c * N + n0 + i] : 0.f;
     }
     const float dsk = live ? d_skip[c] : 0.f;
+
+    float p_dt[SCAN1_PRE], p_bias[SCAN1_PRE], p_bc[SCAN1_PRE_BC];
+    uint32_t p_u[SCAN1_PRE], p_z[SCAN1_PRE];
+    auto load_chunk = [&](int t0) {                    // PRE only
+        const int nt = min(SCAN1_CHUNK, n_tok - t0);
+#pragma unroll
+        for (int y = 0; y < SCAN1_PRE; ++y) {
+            const int i = threadIdx.x + 128 * y;
+            const int tt = i / per_block, cc = c_first + (i - tt * per_block);
+            p_dt[y] = 0.f; p_bias[y] = 0.f; p_u[y] = 0; p_z[y] = 0;
+            if (tt < nt && cc < inner) {
+                const size_t row = (size_t)(start + t0 + tt);
+                p_dt[y] = dt_raw[row * inner + cc];
+                p_bias[y] = dt_bias[cc];
+                p_u[y] = rv_load_raw(u, u_dtype, row * inner + cc);
+                p_z[y] = rv_load_raw(z, z_dtype, row * z_stride + z_col0 + cc);
+            }
+        }
+#pragma unroll
+        for (int y = 0; y < SCAN1_PRE_BC; ++y) {
+            const int i = threadIdx.x + 128 * y;
+            const int tt = i / (2 * N), j = i - tt * 2 * N;
+            p_bc[y] = 0.f;
+            if (tt < nt) p_bc[y] = bc[(size_t)(start + t0 + tt) * bc_stride + (j < N ? b_col0 + j : c_col0 + j - N)];
+        }
+    };
+    const bool pre = PRE && n_tok > SCAN1_CHUNK;         // (a short portion, a decode step's single token: loaded when its turn comes)
+    if (pre) load_chunk(0);
     for (int t0 = 0; t0 < n_tok; t0 += SCAN1_CHUNK) {
         const int nt = min(SCAN1_CHUNK, n_tok - t0);
+        float zs[SCAN1_PRE];                               // PRE: silu(z) of this thread's (token, channel) pairs
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * 2 * N; i += blockDim.x) {
-            const int tt = i / (2 * N), j = i - tt * 2 * N;
-            sBC[i] = bc[(size_t)(start + t0 + tt) * bc_stride + (j < N ? b_col0 + j : c_col0 + j - N)];
-        }
-        for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
-            const int tt = i / per_block, cc = c_first + (i - tt * per_block);
-            float dt = 0.f, uv = 0.f;
-            if (cc < inner) {
-                const size_t row = (size_t)(start + t0 + tt);
-                const float raw = dt_raw[row * inner + cc] + dt_bias[cc];
-                dt = raw > 20.f ? raw : log1pf(expf(raw));
-                uv = rv_load_any(u, u_dtype, row * inner + cc);
+        if (pre) {
+#pragma unroll
+            for (int y = 0; y < SCAN1_PRE_BC; ++y) {
+                const int i = threadIdx.x + 128 * y;
+                if (i < SCAN1_CHUNK * 2 * N) sBC[i] = p_bc[y];
             }
-            sDt[i] = dt;
-            sU[i] = uv;
+#pragma unroll
+            for (int y = 0; y < SCAN1_PRE; ++y) {
+                const int i = threadIdx.x + 128 * y;
+                if (i < SCAN1_CHUNK * per_block) {
+                    const float raw = p_dt[y] + p_bias[y];
+                    const bool real = i < nt * per_block;
+                    sDt[i] = real ? (raw > 20.f ? raw : log1pf(expf(raw))) : 0.f;
+                    sU[i] = rv_raw_value(p_u[y], u_dtype);
+                    const float zv = rv_raw_value(p_z[y], z_dtype);
+                    zs[y] = zv / (1.0f + expf(-zv));
+                }
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * 2 * N; i += blockDim.x) {
+                const int tt = i / (2 * N), j = i - tt * 2 * N;
+                sBC[i] = bc[(size_t)(start + t0 + tt) * bc_stride + (j < N ? b_col0 + j : c_col0 + j - N)];
+            }
+            for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
+                const int tt = i / per_block, cc = c_first + (i - tt * per_block);
+                float dt = 0.f, uv = 0.f;
+                if (cc < inner) {
+                    const size_t row = (size_t)(start + t0 + tt);
+                    const float raw = dt_raw[row * inner + cc] + dt_bias[cc];
+                    dt = raw > 20.f ? raw : log1pf(expf(raw));
+                    uv = rv_load_any(u, u_dtype, row * inner + cc);
+                }
+                sDt[i] = dt;
+                sU[i] = uv;
+            }
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {                   // (threads beyond the last channel walk along: the shuffles need every lane)
+        if (pre && t0 + SCAN1_CHUNK < n_tok) load_chunk(t0 + SCAN1_CHUNK);
+        int tt0 = 0;
+        for (; tt0 + 4 <= nt; tt0 += 4) {                   // (threads beyond the last channel walk along: the shuffles need every lane)
+            float dec[4][NS], dub[4][NS], uv[4], acc[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const float dt = sDt[(tt0 + x) * per_block + cl];
+                uv[x] = sU[(tt0 + x) * per_block + cl];
+                const float du = dt * uv[x];
+                const float* B = sBC + (tt0 + x) * 2 * N + n0;
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    const bool ok = n0 + i < N;
+                    dec[x][i] = expf(dt * a[i]);
+                    dub[x][i] = ok ? du * B[i] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const float* C = sBC + (tt0 + x) * 2 * N + N + n0;
+                acc[x] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    S[i] = fmaf(dec[x][i], S[i], dub[x][i]);
+                    acc[x] = fmaf(S[i], n0 + i < N ? C[i] : 0.f, acc[x]);
+                }
+            }
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                for (int o = 1; o < parts; o <<= 1) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], o);
+                if (part == 0) sU[(tt0 + x) * per_block + cl] = fmaf(dsk, uv[x], acc[x]);
+            }
+        }
+        for (int tt = tt0; tt < nt; ++tt) {                 // the last one to three tokens of a sequence (a decode step's only one)
             const float dt = sDt[tt * per_block + cl];
             const float uv = sU[tt * per_block + cl];
             const float du = dt * uv;
@@ -616,12 +710,21 @@ selective_scan1_kernel(const void* __restrict__ u, int u_dtype, const float* __r
             if (part == 0) sU[tt * per_block + cl] = fmaf(dsk, uv, acc);
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
-            const int tt = i / per_block, cc = c_first + (i - tt * per_block);
-            if (cc < inner) {
-                const size_t row = (size_t)(start + t0 + tt);
-                const float zv = rv_load_any(z, z_dtype, row * z_stride + z_col0 + cc);
-                rv_store_any(out, out_dtype, row * inner + cc, sU[i] * (zv / (1.0f + expf(-zv))));
+        if (pre) {
+#pragma unroll
+            for (int y = 0; y < SCAN1_PRE; ++y) {
+                const int i = threadIdx.x + 128 * y;
+                const int tt = i / per_block, cc = c_first + (i - tt * per_block);
+                if (i < nt * per_block && cc < inner) rv_store_any(out, out_dtype, (size_t)(start + t0 + tt) * inner + cc, sU[i] * zs[y]);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nt * per_block; i += blockDim.x) {
+                const int tt = i / per_block, cc = c_first + (i - tt * per_block);
+                if (cc < inner) {
+                    const size_t row = (size_t)(start + t0 + tt);
+                    const float zv = rv_load_any(z, z_dtype, row * z_stride + z_col0 + cc);
+                    rv_store_any(out, out_dtype, row * inner + cc, sU[i] * (zv / (1.0f + expf(-zv))));
+                }
             }
         }
     }
@@ -650,7 +753,9 @@ RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw
     const int per_block = 128 / parts;
     const size_t smem = (size_t)SCAN1_CHUNK * (2 * N + 2 * per_block) * sizeof(float);
     if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
-    auto kernel = ns == 4 ? selective_scan1_kernel<4> : selective_scan1_kernel<16>;
+    const bool pre = per_block <= 8 * SCAN1_PRE && 2 * N <= 8 * SCAN1_PRE_BC;
+    auto kernel = ns == 4 ? (pre ? selective_scan1_kernel<4, true> : selective_scan1_kernel<4, false>)
+                          : (pre ? selective_scan1_kernel<16, true> : selective_scan1_kernel<16, false>);
     RV_LAUNCH_ST = rv_launch(kernel, dim3((inner + per_block - 1) / per_block, n_seqs), dim3(128), smem, stream, u, u_dtype, dt_raw,
                              dt_bias, A, bc, bc_stride, b_col0, c_col0, d_skip, z, z_dtype, z_stride, z_col0, cu_seqlens, state_slots,
                              state, (size_t)state_stride, out, out_dtype, inner, N, parts);
@@ -668,10 +773,16 @@ RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw
 // meet by shuffles.  Grid (column blocks, heads, sequences), 128 threads.  The unit vectors q and k of DR_CHUNK tokens, and
 // the tokens' g and beta, wait in shared memory; a lane's DR_NS entries of a row start at a multiple of DR_NS + 4 floats, so
 // that the 16-byte reads of the `parts` lanes of a column fall on different banks.  Rows are zero beyond d.
-#define DR_NS 32
+#define DR_NS 16
 #define DR_PAD (DR_NS + 4)
 #define DR_CHUNK 16
+#define DR_PRE_Q 4          // q (and k) elements per lane and token that the prefetch holds: d <= 32 * DR_PRE_Q
+#define DR_PRE_V 8          // values per thread and chunk that the prefetch holds: 128 / parts <= 8 * DR_PRE_V
 
+// PRE: the raw inputs of the next chunk are loaded into registers before the current chunk is walked, so that their way
+// from memory lies behind the walk; without it (wider keys, or more columns per block than the registers hold) a chunk
+// is loaded when its turn comes.
+template <bool PRE>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, const float* __restrict__ proj, int proj_stride,
                   int b_col0, int a_col0, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -692,8 +803,12 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
     float* sV = sBeta + DR_CHUNK;                          // [DR_CHUNK][128 / parts]: the chunk's values of the block's columns
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per_block = 128 / parts;
-    const int col = blockIdx.x * per_block + tid / parts;
-    const int part = tid % parts;
+    // a warp holds 32 / parts neighbouring columns; the `parts` lanes of a column lie 32 / parts lanes apart, so that
+    // neighbouring lanes read and write neighbouring floats of the state
+    const int cpw = 32 / parts;
+    const int colb = warp * cpw + lane % cpw;
+    const int col = blockIdx.x * per_block + colb;
+    const int part = lane / cpw;
     const bool live = col < vd;
     const int n0 = part * DR_NS;
     const int kh = h / (heads / qk_heads);
@@ -705,48 +820,124 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
     for (int i = 0; i < DR_NS; ++i) S[i] = (live && n0 + i < d) ? srow[(size_t)(n0 + i) * vd + col] : 0.f;
     for (int i = tid; i < 2 * DR_CHUNK * row_floats; i += 128) dr_smem[i] = 0.f;      // the padding stays zero from here on
     const float decay_rate = expf(a_log[h]), a_bias = dt_bias[h];
-    for (int t0 = 0; t0 < n_tok; t0 += DR_CHUNK) {
+
+    uint32_t pq[DR_CHUNK / 4][DR_PRE_Q], pk[DR_CHUNK / 4][DR_PRE_Q], pv[DR_PRE_V];      // raw bits: converted when their chunk's turn comes
+    float pb = 0.f, pa = 0.f;
+    auto load_chunk = [&](int t0) {                       // PRE only: the chunk's raw q, k (a warp per token), v, b and a
         const int nt = min(DR_CHUNK, n_tok - t0);
-        __syncthreads();
-        for (int tt = warp; tt < nt; tt += 4) {                       // a warp per token: q and k of the head, made unit vectors
-            const size_t row = (size_t)(start + t0 + tt) * qkv_stride;
-            float sq = 0.f, sk = 0.f;
-            for (int e = lane; e < d; e += 32) {
-                const float qv = rv_load_any(qkv, qkv_dtype, row + (size_t)kh * d + e);
-                const float kv = rv_load_any(qkv, qkv_dtype, row + qk + (size_t)kh * d + e);
-                const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
-                sQ[at] = qv;
-                sK[at] = kv;
-                sq = fmaf(qv, qv, sq);
-                sk = fmaf(kv, kv, sk);
-            }
-            sq = rv_warp_sum(sq);
-            sk = rv_warp_sum(sk);
-            const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
-            for (int e = lane; e < d; e += 32) {                      // every lane rescales what it wrote itself
-                const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
-                sQ[at] *= rq;
-                sK[at] *= rk;
+#pragma unroll
+        for (int x = 0; x < DR_CHUNK / 4; ++x) {
+            const int tt = warp + 4 * x;
+            const size_t row = (size_t)(start + t0 + tt) * qkv_stride + (size_t)kh * d;
+#pragma unroll
+            for (int y = 0; y < DR_PRE_Q; ++y) {
+                const int e = lane + 32 * y;
+                pq[x][y] = 0; pk[x][y] = 0;
+                if (tt < nt && e < d) {
+                    pq[x][y] = rv_load_raw(qkv, qkv_dtype, row + e);
+                    pk[x][y] = rv_load_raw(qkv, qkv_dtype, row + qk + e);
+                }
             }
         }
-        for (int i = tid; i < nt * per_block; i += 128) {
+#pragma unroll
+        for (int y = 0; y < DR_PRE_V; ++y) {
+            const int i = tid + 128 * y;
             const int tt = i / per_block, cc = blockIdx.x * per_block + (i - tt * per_block);
-            sV[i] = cc < vd ? rv_load_any(qkv, qkv_dtype, (size_t)(start + t0 + tt) * qkv_stride + 2 * qk + (size_t)h * vd + cc) : 0.f;
+            pv[y] = 0;
+            if (tt < nt && cc < vd) pv[y] = rv_load_raw(qkv, qkv_dtype, (size_t)(start + t0 + tt) * qkv_stride + 2 * qk + (size_t)h * vd + cc);
         }
         if (tid < nt) {
             const size_t row = (size_t)(start + t0 + tid) * proj_stride;
-            const float b = proj[row + b_col0 + h];
-            const float a = proj[row + a_col0 + h] + a_bias;
-            const float sp = a > 20.f ? a : log1pf(expf(a));
-            sBeta[tid] = 1.0f / (1.0f + expf(-b));
-            sG[tid] = expf(-decay_rate * sp);
+            pb = proj[row + b_col0 + h];
+            pa = proj[row + a_col0 + h];
+        }
+    };
+    const bool pre = PRE && n_tok > DR_CHUNK;           // (a short portion, a decode step's single token: loaded when its turn comes)
+    if (pre) load_chunk(0);
+    for (int t0 = 0; t0 < n_tok; t0 += DR_CHUNK) {
+        const int nt = min(DR_CHUNK, n_tok - t0);
+        __syncthreads();
+        if (pre) {
+#pragma unroll
+            for (int x = 0; x < DR_CHUNK / 4; ++x) {
+                const int tt = warp + 4 * x;                                  // (a warp-uniform test)
+                if (tt < nt) {
+                    float sq = 0.f, sk = 0.f, fq[DR_PRE_Q], fk[DR_PRE_Q];
+#pragma unroll
+                    for (int y = 0; y < DR_PRE_Q; ++y) {
+                        fq[y] = rv_raw_value(pq[x][y], qkv_dtype);
+                        fk[y] = rv_raw_value(pk[x][y], qkv_dtype);
+                        sq = fmaf(fq[y], fq[y], sq);
+                        sk = fmaf(fk[y], fk[y], sk);
+                    }
+                    sq = rv_warp_sum(sq);
+                    sk = rv_warp_sum(sk);
+                    const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
+#pragma unroll
+                    for (int y = 0; y < DR_PRE_Q; ++y) {
+                        const int e = lane + 32 * y;
+                        if (e < d) {
+                            const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                            sQ[at] = fq[y] * rq;
+                            sK[at] = fk[y] * rk;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int y = 0; y < DR_PRE_V; ++y) {
+                const int i = tid + 128 * y;
+                if (i < DR_CHUNK * per_block) sV[i] = rv_raw_value(pv[y], qkv_dtype);       // (zero beyond the sequence)
+            }
+            if (tid < DR_CHUNK) {                          // beyond the sequence: beta 0 and decay 1 leave the state as it is
+                const float a = pa + a_bias;
+                const float sp = a > 20.f ? a : log1pf(expf(a));
+                sBeta[tid] = tid < nt ? 1.0f / (1.0f + expf(-pb)) : 0.f;
+                sG[tid] = tid < nt ? expf(-decay_rate * sp) : 1.f;
+            }
+        } else {
+            for (int tt = warp; tt < nt; tt += 4) {                       // a warp per token: q and k of the head, made unit vectors
+                const size_t row = (size_t)(start + t0 + tt) * qkv_stride;
+                float sq = 0.f, sk = 0.f;
+                for (int e = lane; e < d; e += 32) {
+                    const float qv = rv_load_any(qkv, qkv_dtype, row + (size_t)kh * d + e);
+                    const float kv = rv_load_any(qkv, qkv_dtype, row + qk + (size_t)kh * d + e);
+                    const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                    sQ[at] = qv;
+                    sK[at] = kv;
+                    sq = fmaf(qv, qv, sq);
+                    sk = fmaf(kv, kv, sk);
+                }
+                sq = rv_warp_sum(sq);
+                sk = rv_warp_sum(sk);
+                const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
+                for (int e = lane; e < d; e += 32) {                      // every lane rescales what it wrote itself
+                    const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                    sQ[at] *= rq;
+                    sK[at] *= rk;
+                }
+            }
+            for (int i = tid; i < nt * per_block; i += 128) {
+                const int tt = i / per_block, cc = blockIdx.x * per_block + (i - tt * per_block);
+                sV[i] = cc < vd ? rv_load_any(qkv, qkv_dtype, (size_t)(start + t0 + tt) * qkv_stride + 2 * qk + (size_t)h * vd + cc) : 0.f;
+            }
+            if (tid < nt) {
+                const size_t row = (size_t)(start + t0 + tid) * proj_stride;
+                const float b = proj[row + b_col0 + h];
+                const float a = proj[row + a_col0 + h] + a_bias;
+                const float sp = a > 20.f ? a : log1pf(expf(a));
+                sBeta[tid] = 1.0f / (1.0f + expf(-b));
+                sG[tid] = expf(-decay_rate * sp);
+            }
         }
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {                   // (threads beyond the last column walk along: the shuffles need every lane)
+        if (pre && t0 + DR_CHUNK < n_tok) load_chunk(t0 + DR_CHUNK);
+        // (threads beyond the last column walk along: the shuffles need every lane)
+        auto step = [&](int tt) {
             const size_t trow = (size_t)(start + t0 + tt);
             const float4* K4 = reinterpret_cast<const float4*>(sK + tt * row_floats + part * DR_PAD);
             const float4* Q4 = reinterpret_cast<const float4*>(sQ + tt * row_floats + part * DR_PAD);
-            const float vv = sV[tt * per_block + tid / parts];
+            const float vv = sV[tt * per_block + colb];
             float kreg[DR_NS];
             float ac[4] = {0.f, 0.f, 0.f, 0.f};                // four sums side by side: the chain of a column is a quarter as long
 #pragma unroll
@@ -757,7 +948,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
                 ac[2] = fmaf(S[4 * i + 2], k4.z, ac[2]); ac[3] = fmaf(S[4 * i + 3], k4.w, ac[3]);
             }
             float acc = (ac[0] + ac[1]) + (ac[2] + ac[3]);
-            for (int o = 1; o < parts; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            for (int o = cpw; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             const float g = sG[tt];
             const float u = sBeta[tt] * (vv - g * acc);
             float ov4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -770,8 +961,14 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
                 S[4 * i + 3] = fmaf(g, S[4 * i + 3], kreg[4 * i + 3] * u); ov4[3] = fmaf(S[4 * i + 3], q4.w, ov4[3]);
             }
             float ov = (ov4[0] + ov4[1]) + (ov4[2] + ov4[3]);
-            for (int o = 1; o < parts; o <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
-            if (part == 0 && live) out[trow * heads * vd + (size_t)h * vd + col] = ov;
+            for (int o = cpw; o < 32; o <<= 1) ov += __shfl_xor_sync(0xffffffffu, ov, o);
+            if (part == 0 && live && tt < nt) out[trow * heads * vd + (size_t)h * vd + col] = ov;
+        };
+        if (nt == DR_CHUNK) {                              // a whole chunk: neighbouring tokens may run into one another
+#pragma unroll 4
+            for (int tt = 0; tt < DR_CHUNK; ++tt) step(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) step(tt);
         }
     }
     if (live) {
@@ -800,7 +997,8 @@ RV_EXPORT int rv_delta_rule(const void* qkv, int qkv_dtype, int qkv_stride, cons
     const int per_block = 128 / parts;
     const size_t smem = sizeof(float) * (2 * (size_t)DR_CHUNK * parts * DR_PAD + 2 * DR_CHUNK + (size_t)DR_CHUNK * per_block);
     if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
-    RV_LAUNCH_ST = rv_launch(delta_rule_kernel, dim3((vd + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, qkv,
+    const bool pre = d <= 32 * DR_PRE_Q && per_block <= 8 * DR_PRE_V;
+    RV_LAUNCH_ST = rv_launch(pre ? delta_rule_kernel<true> : delta_rule_kernel<false>, dim3((vd + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, qkv,
                              qkv_dtype, qkv_stride, proj, proj_stride, b_col0, a_col0, a_log, dt_bias, cu_seqlens, state_slots, state,
                              (size_t)state_stride, out, heads, qk_heads, d, vd, parts, unit_eps);
     return rv_launch_status();

@@ -324,6 +324,59 @@ ta_split_scores_kernel(const T* __restrict__ q, const T* __restrict__ cache, con
     const size_t page_elems = (size_t)nkv * page_size * (hd + vd);
     const bool biased = r1 != nullptr;
     const size_t stride = (size_t)nsplit * span;
+    if constexpr (VEC && sizeof(T) == 2) {
+        if (rep % 4 == 0) {
+            // a warp per block of four heads of one key/value head, a lane per key: the key's row is read once, 16 bytes at a time
+            for (int hb = warp; hb < nh / 4; hb += TA_WARPS) {
+                const int h0 = hb * 4, kvh = h0 / rep;
+                float m[4], l[4], a1[4], a2[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    m[x] = -INFINITY; l[x] = 0.f;
+                    a1[x] = biased ? r1[h0 + x] : 0.f; a2[x] = biased ? r2[h0 + x] : 0.f;
+                }
+                for (int j = w.k0 + lane; j < w.k1; j += 32) {
+                    const T* kp = cache + (size_t)w.table[j / page_size] * page_elems + ((size_t)kvh * page_size + (j % page_size)) * hd;
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int e = 0; e < hd; e += 8) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(kp + e);
+                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                        const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+                        const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const float* qx = qs + (size_t)(h0 + x) * hd + e;
+                            const float4 qa = *reinterpret_cast<const float4*>(qx), qb = *reinterpret_cast<const float4*>(qx + 4);
+                            float sacc = acc[x];
+                            sacc = fmaf(f0.x, qa.x, sacc); sacc = fmaf(f0.y, qa.y, sacc); sacc = fmaf(f1.x, qa.z, sacc); sacc = fmaf(f1.y, qa.w, sacc);
+                            sacc = fmaf(f2.x, qb.x, sacc); sacc = fmaf(f2.y, qb.y, sacc); sacc = fmaf(f3.x, qb.z, sacc); sacc = fmaf(f3.y, qb.w, sacc);
+                            acc[x] = sacc;
+                        }
+                    }
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        float sc = acc[x] * scale;
+                        if (biased) sc -= a1[x] * log1pf(a2[x] * (float)(w.pos - j));
+                        S[((size_t)t * nh + h0 + x) * stride + (j - w.lo)] = sc;
+                        const float m_new = fmaxf(m[x], sc);
+                        l[x] = l[x] * expf(m[x] - m_new) + expf(sc - m_new);
+                        m[x] = m_new;
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float M = rv_warp_max(m[x]);
+                    const float L = rv_warp_sum(m[x] == -INFINITY ? 0.f : l[x] * expf(m[x] - M));
+                    if (lane == 0) {
+                        float* st = stats + (((size_t)t * nsplit + sp) * nh + h0 + x) * 2;
+                        st[0] = M;
+                        st[1] = L;
+                    }
+                }
+            }
+            return;
+        }
+    }
     for (int h = warp; h < nh; h += TA_WARPS) {
         const float a1 = biased ? r1[h] : 0.f, a2 = biased ? r2[h] : 0.f;
         float* row = S + ((size_t)t * nh + h) * stride;
@@ -387,6 +440,7 @@ ta_split_apply_kernel(const T* __restrict__ cache, const int* __restrict__ block
 
     constexpr int EV = VEC ? 16 / (int)sizeof(T) : 1;      // value elements per thread and key
     const int vblocks = vd / EV;
+    const bool quads = VEC && sizeof(T) == 2 && rep % 4 == 0;
     for (int j0 = w.k0; j0 < w.k1; j0 += TA_TILE) {
         const int nk = min(TA_TILE, w.k1 - j0);
         for (int i = tid; i < nh * TA_TILE; i += TA_THREADS) {
@@ -406,6 +460,36 @@ ta_split_apply_kernel(const T* __restrict__ cache, const int* __restrict__ block
                 PM[i] = a;
             }
             __syncthreads();
+        }
+        if (quads) {
+            // four heads of one key/value head and four value elements per thread: every value of the tile is read once
+            const int v4 = vd / 4;
+            for (int i = tid; i < (nh / 4) * v4; i += TA_THREADS) {
+                const int hb = i / v4, e = (i - hb * v4) * 4, h0 = hb * 4;
+                const size_t head_off = (size_t)(h0 / rep) * page_size * vd + e;
+                float acc[4][4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float4 o4 = *reinterpret_cast<const float4*>(Os + (h0 + x) * vd + e);
+                    acc[x][0] = o4.x; acc[x][1] = o4.y; acc[x][2] = o4.z; acc[x][3] = o4.w;
+                }
+                for (int jj = 0; jj < nk; ++jj) {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(cache + vrow[jj] + head_off);
+                    const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const float p = PM[(h0 + x) * TA_TILE + jj];
+                        acc[x][0] = fmaf(p, fa.x, acc[x][0]); acc[x][1] = fmaf(p, fa.y, acc[x][1]);
+                        acc[x][2] = fmaf(p, fb.x, acc[x][2]); acc[x][3] = fmaf(p, fb.y, acc[x][3]);
+                    }
+                }
+#pragma unroll
+                for (int x = 0; x < 4; ++x)
+                    *reinterpret_cast<float4*>(Os + (h0 + x) * vd + e) = make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
+            }
+            __syncthreads();
+            continue;
         }
         for (int i = tid; i < nh * vblocks; i += TA_THREADS) {
             const int h = i / vblocks, e = (i - h * vblocks) * EV;
@@ -451,7 +535,7 @@ ta_split_join_kernel(const float* __restrict__ part, const int* __restrict__ cu_
     rv_pdl_wait();
     const int t = blockIdx.x;
     const TaWhere w = ta_where(nullptr, cu_seqlens, ctx_lens, token_seq, t, 0, span, chunk, 0);
-    for (int i = threadIdx.x; i < width; i += TA_THREADS) {
+    for (int i = blockIdx.y * TA_THREADS + threadIdx.x; i < width; i += gridDim.y * TA_THREADS) {
         float a = 0.f;
         for (int s = 0; s < w.nvalid; ++s) a += part[((size_t)t * nsplit + s) * width + i];
         out[(size_t)t * width + i] = rv_from_float<T>(a);
@@ -475,7 +559,7 @@ static int ta_split_launch(int which, const void* q, const void* cache, const in
                              block_tables, cu_seqlens, ctx_lens, token_seq, (const float*)S, (const float*)stats, talk, part, nh, nkv, hd, vd,
                              page_size, max_blocks, chunk, span, nsplit);
     if (rv_launch_status() != RV_OK) return rv_launch_status();
-    RV_LAUNCH_ST = rv_launch(ta_split_join_kernel<T>, dim3(n_tokens), dim3(TA_THREADS), 0, stream, (const float*)part, cu_seqlens, ctx_lens,
+    RV_LAUNCH_ST = rv_launch(ta_split_join_kernel<T>, dim3(n_tokens, (nh * vd + TA_THREADS - 1) / TA_THREADS), dim3(TA_THREADS), 0, stream, (const float*)part, cu_seqlens, ctx_lens,
                              token_seq, (T*)out, nh * vd, chunk, span, nsplit);
     return rv_launch_status();
 }

@@ -59,17 +59,22 @@ struct TmArgs {
 // key/value heads into `dst` [nkv][TA_BN][width + 8]
 __device__ __forceinline__ void tm_fetch(__nv_bfloat16* dst, const TmArgs& a, const int* table, int j0, int j_end, int width, size_t kind_off,
                                          int tid, int nthreads) {
+    // eight lanes per row: the row's place in the cache is worked out once, then the lanes copy its 16-byte pieces
     const int chunks = width / 8, ld = width + 8;
-    const int total = a.nkv * TA_BN * chunks;
+    const int rows = a.nkv * TA_BN;
     const size_t page_elems = (size_t)a.nkv * a.page_size * (a.hd + a.vd);
-    for (int i = tid; i < total; i += nthreads) {
-        const int c = i % chunks, rowi = i / chunks;
+    const int l8 = tid & 7;
+    for (int rowi = tid >> 3; rowi < rows; rowi += nthreads >> 3) {
         const int jj = rowi % TA_BN, g = rowi / TA_BN;
         const int j = j0 + jj;
         const bool real = j <= j_end;
         const __nv_bfloat16* src = a.cache;
-        if (real) src += (size_t)table[j / a.page_size] * page_elems + kind_off + ((size_t)g * a.page_size + (j % a.page_size)) * width + c * 8;
-        tm_cp16(dst + ((size_t)g * TA_BN + jj) * ld + c * 8, src, real);
+        if (real) {
+            const int pg = j / a.page_size;
+            src += (size_t)table[pg] * page_elems + kind_off + ((size_t)g * a.page_size + (j - pg * a.page_size)) * width;
+        }
+        __nv_bfloat16* d = dst + ((size_t)g * TA_BN + jj) * ld;
+        for (int c = l8; c < chunks; c += 8) tm_cp16(d + c * 8, real ? src + c * 8 : src, real);
     }
 }
 
@@ -168,7 +173,7 @@ talking_attention_mma_kernel(const TmArgs a) {
             for (int x = 0; x < 4; ++x) {
                 const int rr = x >> 1, j = j0 + nt * 8 + c0 + (x & 1);
                 float v = s[nt][x] * a.scale;
-                if (a.r1) v -= row_r1[rr] * log1pf(row_r2[rr] * (float)(row_pos[rr] - j));
+                if (a.r1) v -= row_r1[rr] * __logf(1.0f + row_r2[rr] * (float)(row_pos[rr] - j));
                 s[nt][x] = (row_ok[rr] && j <= row_pos[rr] && j >= row_lo[rr]) ? v : -INFINITY;
             }
         }
