@@ -59,22 +59,25 @@ struct TmArgs {
 // key/value heads into `dst` [nkv][TA_BN][width + 8]
 __device__ __forceinline__ void tm_fetch(__nv_bfloat16* dst, const TmArgs& a, const int* table, int j0, int j_end, int width, size_t kind_off,
                                          int tid, int nthreads) {
-    // eight lanes per row: the row's place in the cache is worked out once, then the lanes copy its 16-byte pieces
+    // two lanes per row (a pair copies one 32-byte sector per step): the row's place in the cache is worked out once
     const int chunks = width / 8, ld = width + 8;
     const int rows = a.nkv * TA_BN;
     const size_t page_elems = (size_t)a.nkv * a.page_size * (a.hd + a.vd);
-    const int l8 = tid & 7;
-    for (int rowi = tid >> 3; rowi < rows; rowi += nthreads >> 3) {
+    const int l2 = tid & 1;
+    for (int rowi = tid >> 1; rowi < rows; rowi += nthreads >> 1) {
         const int jj = rowi % TA_BN, g = rowi / TA_BN;
         const int j = j0 + jj;
         const bool real = j <= j_end;
         const __nv_bfloat16* src = a.cache;
         if (real) {
             const int pg = j / a.page_size;
-            src += (size_t)table[pg] * page_elems + kind_off + ((size_t)g * a.page_size + (j - pg * a.page_size)) * width;
+            src += (size_t)table[pg] * page_elems + kind_off + ((size_t)g * a.page_size + (j - pg * a.page_size)) * width + l2 * 8;
         }
-        __nv_bfloat16* d = dst + ((size_t)g * TA_BN + jj) * ld;
-        for (int c = l8; c < chunks; c += 8) tm_cp16(d + c * 8, real ? src + c * 8 : src, real);
+        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + ((size_t)g * TA_BN + jj) * ld + l2 * 8);
+        const int n = real ? 16 : 0, step = real ? 16 : 0;
+        for (int c = l2; c < chunks; c += 2) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d + (c - l2) * 16), "l"(src + (c - l2) * (step / 2)), "r"(n) : "memory");
+        }
     }
 }
 
@@ -145,14 +148,16 @@ talking_attention_mma_kernel(const TmArgs a) {
             sT[i] = h < nh ? a.talk[h * nh + gg] : 0.f;
         }
 
-    const __nv_bfloat16* myK = sK + (size_t)g * TA_BN * ldk;
+    const size_t my_k_off = (size_t)g * TA_BN * ldk;
     const __nv_bfloat16* myV = sV + (size_t)g * TA_BN * ldv;
     __nv_bfloat16* myPM = sPM + (size_t)warp * 16 * ldp;
     const size_t v_off = (size_t)nkv * a.page_size * hd;
     const int mi = lane >> 3, mr = lane & 7;
 
     // the scores of the warp's 16 rows against the tile's keys, bias taken off, hidden keys at -inf
-    auto scores = [&](float (&s)[TA_BN / 8][4], int j0) {
+    const int lo_max = a.chunk > 0 ? (pos_last / a.chunk) * a.chunk : 0;
+    auto scores = [&](float (&s)[TA_BN / 8][4], int j0, const __nv_bfloat16* myK) {
+        const bool open = n_tok == CT && j0 + TA_BN - 1 <= pos0 && j0 >= lo_max;      // every key of the tile is seen by every row
 #pragma unroll
         for (int nt = 0; nt < TA_BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
@@ -174,23 +179,37 @@ talking_attention_mma_kernel(const TmArgs a) {
                 const int rr = x >> 1, j = j0 + nt * 8 + c0 + (x & 1);
                 float v = s[nt][x] * a.scale;
                 if (a.r1) v -= row_r1[rr] * __logf(1.0f + row_r2[rr] * (float)(row_pos[rr] - j));
-                s[nt][x] = (row_ok[rr] && j <= row_pos[rr] && j >= row_lo[rr]) ? v : -INFINITY;
+                s[nt][x] = (open || (row_ok[rr] && j <= row_pos[rr] && j >= row_lo[rr])) ? v : -INFINITY;
             }
         }
     };
 
     // ---- walk 1: maxima and denominators
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // (the value tile's place is free in this walk: where it is large enough the key tiles alternate between the two, and
+    // the next tile is on its way while this one is used)
+    const bool two = vd >= hd;
     tm_fetch(sK, a, table, lo_min, pos_last, hd, 0, tid, nthreads);
     tm_commit();
-    for (int j0 = lo_min; j0 <= pos_last; j0 += TA_BN) {
-        tm_wait<0>();
+    int turn = 0;
+    for (int j0 = lo_min; j0 <= pos_last; j0 += TA_BN, turn ^= 1) {
+        const bool more = j0 + TA_BN <= pos_last;
+        __nv_bfloat16* cur = (two && turn) ? sV : sK;
+        if (two) {
+            if (more) tm_fetch(turn ? sK : sV, a, table, j0 + TA_BN, pos_last, hd, 0, tid, nthreads);
+            tm_commit();
+            tm_wait<1>();
+        } else {
+            tm_wait<0>();
+        }
         __syncthreads();
         float s[TA_BN / 8][4];
-        scores(s, j0);
+        scores(s, j0, cur + my_k_off);
         __syncthreads();
-        if (j0 + TA_BN <= pos_last) tm_fetch(sK, a, table, j0 + TA_BN, pos_last, hd, 0, tid, nthreads);
-        tm_commit();
+        if (!two) {
+            if (more) tm_fetch(sK, a, table, j0 + TA_BN, pos_last, hd, 0, tid, nthreads);
+            tm_commit();
+        }
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             float mx = m[rr];
@@ -234,7 +253,7 @@ talking_attention_mma_kernel(const TmArgs a) {
         __syncthreads();
         {
             float s[TA_BN / 8][4];
-            scores(s, j0);
+            scores(s, j0, sK + my_k_off);
 #pragma unroll
             for (int nt = 0; nt < TA_BN / 8; ++nt) {
 #pragma unroll
