@@ -769,12 +769,10 @@ RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw
 //     beta = sigmoid(b),   g = exp(-exp(A_log_h) softplus(a + dt_bias_h))
 //     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
 // Every step of the rule acts on the columns of S one by one, so a column is one thread's work (no exchange between
-// columns): a column's d entries live in the registers of `parts` neighbouring lanes, DR_NS each, whose partial sums
+// columns): a column's d entries live in the registers of `parts` lanes, NS each, whose partial sums
 // meet by shuffles.  Grid (column blocks, heads, sequences), 128 threads.  The unit vectors q and k of DR_CHUNK tokens, and
-// the tokens' g and beta, wait in shared memory; a lane's DR_NS entries of a row start at a multiple of DR_NS + 4 floats, so
+// the tokens' g and beta, wait in shared memory; a lane's NS entries of a row start at a multiple of NS + 4 floats, so
 // that the 16-byte reads of the `parts` lanes of a column fall on different banks.  Rows are zero beyond d.
-#define DR_NS 16
-#define DR_PAD (DR_NS + 4)
 #define DR_CHUNK 16
 #define DR_PRE_Q 4          // q (and k) elements per lane and token that the prefetch holds: d <= 32 * DR_PRE_Q
 #define DR_PRE_V 8          // values per thread and chunk that the prefetch holds: 128 / parts <= 8 * DR_PRE_V
@@ -782,7 +780,8 @@ RV_EXPORT int rv_selective_scan1(const void* u, int u_dtype, const float* dt_raw
 // PRE: the raw inputs of the next chunk are loaded into registers before the current chunk is walked, so that their way
 // from memory lies behind the walk; without it (wider keys, or more columns per block than the registers hold) a chunk
 // is loaded when its turn comes.
-template <bool PRE>
+// NS: entries of a column per lane (8, 16 or 32: a key of up to 4 NS entries lies in four lanes).
+template <int NS, bool PRE>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, const float* __restrict__ proj, int proj_stride,
                   int b_col0, int a_col0, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
@@ -795,7 +794,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
     const int slot = state_slots[seq];
     if (slot < 0) return;
     const int start = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - start;
-    const int row_floats = parts * DR_PAD;
+    const int row_floats = parts * (NS + 4);
     float* sQ = dr_smem;                                   // [DR_CHUNK][row_floats]
     float* sK = sQ + DR_CHUNK * row_floats;
     float* sG = sK + DR_CHUNK * row_floats;                // [DR_CHUNK]
@@ -810,14 +809,14 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
     const int col = blockIdx.x * per_block + colb;
     const int part = lane / cpw;
     const bool live = col < vd;
-    const int n0 = part * DR_NS;
+    const int n0 = part * NS;
     const int kh = h / (heads / qk_heads);
     const int qk = qk_heads * d;
     const float q_scale = rsqrtf((float)d);
-    float S[DR_NS];
+    float S[NS];
     float* srow = state + (size_t)slot * state_stride + (size_t)h * d * vd;
 #pragma unroll
-    for (int i = 0; i < DR_NS; ++i) S[i] = (live && n0 + i < d) ? srow[(size_t)(n0 + i) * vd + col] : 0.f;
+    for (int i = 0; i < NS; ++i) S[i] = (live && n0 + i < d) ? srow[(size_t)(n0 + i) * vd + col] : 0.f;
     for (int i = tid; i < 2 * DR_CHUNK * row_floats; i += 128) dr_smem[i] = 0.f;      // the padding stays zero from here on
     const float decay_rate = expf(a_log[h]), a_bias = dt_bias[h];
 
@@ -877,7 +876,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
                     for (int y = 0; y < DR_PRE_Q; ++y) {
                         const int e = lane + 32 * y;
                         if (e < d) {
-                            const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                            const int at = tt * row_floats + (e / NS) * (NS + 4) + (e % NS);
                             sQ[at] = fq[y] * rq;
                             sK[at] = fk[y] * rk;
                         }
@@ -902,7 +901,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
                 for (int e = lane; e < d; e += 32) {
                     const float qv = rv_load_any(qkv, qkv_dtype, row + (size_t)kh * d + e);
                     const float kv = rv_load_any(qkv, qkv_dtype, row + qk + (size_t)kh * d + e);
-                    const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                    const int at = tt * row_floats + (e / NS) * (NS + 4) + (e % NS);
                     sQ[at] = qv;
                     sK[at] = kv;
                     sq = fmaf(qv, qv, sq);
@@ -912,7 +911,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
                 sk = rv_warp_sum(sk);
                 const float rq = q_scale / sqrtf(sq + unit_eps), rk = 1.0f / sqrtf(sk + unit_eps);
                 for (int e = lane; e < d; e += 32) {                      // every lane rescales what it wrote itself
-                    const int at = tt * row_floats + (e / DR_NS) * DR_PAD + (e % DR_NS);
+                    const int at = tt * row_floats + (e / NS) * (NS + 4) + (e % NS);
                     sQ[at] *= rq;
                     sK[at] *= rk;
                 }
@@ -935,13 +934,13 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
         // (threads beyond the last column walk along: the shuffles need every lane)
         auto step = [&](int tt) {
             const size_t trow = (size_t)(start + t0 + tt);
-            const float4* K4 = reinterpret_cast<const float4*>(sK + tt * row_floats + part * DR_PAD);
-            const float4* Q4 = reinterpret_cast<const float4*>(sQ + tt * row_floats + part * DR_PAD);
+            const float4* K4 = reinterpret_cast<const float4*>(sK + tt * row_floats + part * (NS + 4));
+            const float4* Q4 = reinterpret_cast<const float4*>(sQ + tt * row_floats + part * (NS + 4));
             const float vv = sV[tt * per_block + colb];
-            float kreg[DR_NS];
+            float kreg[NS];
             float ac[4] = {0.f, 0.f, 0.f, 0.f};                // four sums side by side: the chain of a column is a quarter as long
 #pragma unroll
-            for (int i = 0; i < DR_NS / 4; ++i) {
+            for (int i = 0; i < NS / 4; ++i) {
                 const float4 k4 = K4[i];
                 kreg[4 * i] = k4.x; kreg[4 * i + 1] = k4.y; kreg[4 * i + 2] = k4.z; kreg[4 * i + 3] = k4.w;
                 ac[0] = fmaf(S[4 * i], k4.x, ac[0]); ac[1] = fmaf(S[4 * i + 1], k4.y, ac[1]);
@@ -953,7 +952,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
             const float u = sBeta[tt] * (vv - g * acc);
             float ov4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < DR_NS / 4; ++i) {
+            for (int i = 0; i < NS / 4; ++i) {
                 const float4 q4 = Q4[i];
                 S[4 * i] = fmaf(g, S[4 * i], kreg[4 * i] * u);             ov4[0] = fmaf(S[4 * i], q4.x, ov4[0]);
                 S[4 * i + 1] = fmaf(g, S[4 * i + 1], kreg[4 * i + 1] * u); ov4[1] = fmaf(S[4 * i + 1], q4.y, ov4[1]);
@@ -973,7 +972,7 @@ delta_rule_kernel(const void* __restrict__ qkv, int qkv_dtype, int qkv_stride, c
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < DR_NS; ++i)
+        for (int i = 0; i < NS; ++i)
             if (n0 + i < d) srow[(size_t)(n0 + i) * vd + col] = S[i];
     }
 }
@@ -984,7 +983,7 @@ RV_EXPORT int rv_delta_rule(const void* qkv, int qkv_dtype, int qkv_stride, cons
                             int a_col0, const float* a_log, const float* dt_bias, const int* cu_seqlens, const int* state_slots,
                             float* state, long long state_stride, float* out, int n_seqs, int heads, int qk_heads, int d, int vd,
                             float unit_eps, cudaStream_t stream) {
-    if (n_seqs < 0 || heads <= 0 || qk_heads <= 0 || heads % qk_heads || d <= 0 || d > 32 * DR_NS || vd <= 0 || n_seqs > 65535 ||
+    if (n_seqs < 0 || heads <= 0 || qk_heads <= 0 || heads % qk_heads || d <= 0 || d > 32 * 32 || vd <= 0 || n_seqs > 65535 ||
         heads > 65535)
         return RV_ERR_BAD_SIZE;
     if (qkv_stride < 2 * qk_heads * d + heads * vd || b_col0 < 0 || a_col0 < 0 || b_col0 + heads > proj_stride ||
@@ -992,13 +991,17 @@ RV_EXPORT int rv_delta_rule(const void* qkv, int qkv_dtype, int qkv_stride, cons
         return RV_ERR_BAD_SIZE;
     if (qkv_dtype & ~1) return RV_ERR_BAD_DTYPE;
     if (n_seqs == 0) return RV_OK;
+    const int ns = d > 64 ? 32 : (d > 32 ? 16 : 8);    // four lanes per column up to a key size of 128
     int parts = 1;
-    while (parts * DR_NS < d) parts <<= 1;             // a power of two of at most 32 lanes of one warp
+    while (parts * ns < d) parts <<= 1;                // a power of two of at most 32 lanes of one warp
     const int per_block = 128 / parts;
-    const size_t smem = sizeof(float) * (2 * (size_t)DR_CHUNK * parts * DR_PAD + 2 * DR_CHUNK + (size_t)DR_CHUNK * per_block);
+    const size_t smem = sizeof(float) * (2 * (size_t)DR_CHUNK * parts * (ns + 4) + 2 * DR_CHUNK + (size_t)DR_CHUNK * per_block);
     if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
     const bool pre = d <= 32 * DR_PRE_Q && per_block <= 8 * DR_PRE_V;
-    RV_LAUNCH_ST = rv_launch(pre ? delta_rule_kernel<true> : delta_rule_kernel<false>, dim3((vd + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, qkv,
+    auto kernel = ns == 32 ? (pre ? delta_rule_kernel<32, true> : delta_rule_kernel<32, false>)
+                : ns == 16 ? (pre ? delta_rule_kernel<16, true> : delta_rule_kernel<16, false>)
+                           : (pre ? delta_rule_kernel<8, true> : delta_rule_kernel<8, false>);
+    RV_LAUNCH_ST = rv_launch(kernel, dim3((vd + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, qkv,
                              qkv_dtype, qkv_stride, proj, proj_stride, b_col0, a_col0, a_log, dt_bias, cu_seqlens, state_slots, state,
                              (size_t)state_stride, out, heads, qk_heads, d, vd, parts, unit_eps);
     return rv_launch_status();

@@ -319,9 +319,20 @@ ta_split_scores_kernel(const T* __restrict__ q, const T* __restrict__ cache, con
     const TaWhere w = ta_where(block_tables, cu_seqlens, ctx_lens, token_seq, t, sp, span, chunk, max_blocks);
     if (w.ctx <= 0 || w.k0 > w.pos) return;
     for (int i = tid; i < nh * hd; i += TA_THREADS) qs[i] = rv_to_float(q[(size_t)t * nh * hd + i]);
-    __syncthreads();
     const int rep = nh / nkv;
     const size_t page_elems = (size_t)nkv * page_size * (hd + vd);
+    {   // the range's value rows are asked into L2 now: the next launch reads them while this one still works on the keys
+        const int lines = (int)((vd * sizeof(T) + 127) / 128);
+        const int total = (w.k1 - w.k0) * nkv * lines;
+        for (int i = tid; i < total; i += TA_THREADS) {
+            const int ln = i % lines, rest = i / lines;
+            const int g = rest % nkv, j = w.k0 + rest / nkv;
+            const T* vp = cache + (size_t)w.table[j / page_size] * page_elems + (size_t)nkv * page_size * hd +
+                          ((size_t)g * page_size + (j % page_size)) * vd;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(vp) + ln * 128));
+        }
+    }
+    __syncthreads();
     const bool biased = r1 != nullptr;
     const size_t stride = (size_t)nsplit * span;
     if constexpr (VEC && sizeof(T) == 2) {
@@ -338,19 +349,27 @@ ta_split_scores_kernel(const T* __restrict__ q, const T* __restrict__ cache, con
                 for (int j = w.k0 + lane; j < w.k1; j += 32) {
                     const T* kp = cache + (size_t)w.table[j / page_size] * page_elems + ((size_t)kvh * page_size + (j % page_size)) * hd;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int e = 0; e < hd; e += 8) {
-                        const uint4 raw = *reinterpret_cast<const uint4*>(kp + e);
-                        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                        const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
-                        const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+                    for (int e0 = 0; e0 < hd; e0 += 32) {               // four 16-byte pieces of the row on their way at a time
+                        uint4 raw4[4];
 #pragma unroll
-                        for (int x = 0; x < 4; ++x) {
-                            const float* qx = qs + (size_t)(h0 + x) * hd + e;
-                            const float4 qa = *reinterpret_cast<const float4*>(qx), qb = *reinterpret_cast<const float4*>(qx + 4);
-                            float sacc = acc[x];
-                            sacc = fmaf(f0.x, qa.x, sacc); sacc = fmaf(f0.y, qa.y, sacc); sacc = fmaf(f1.x, qa.z, sacc); sacc = fmaf(f1.y, qa.w, sacc);
-                            sacc = fmaf(f2.x, qb.x, sacc); sacc = fmaf(f2.y, qb.y, sacc); sacc = fmaf(f3.x, qb.z, sacc); sacc = fmaf(f3.y, qb.w, sacc);
-                            acc[x] = sacc;
+                        for (int y = 0; y < 4; ++y) raw4[y] = e0 + 8 * y < hd ? *reinterpret_cast<const uint4*>(kp + e0 + 8 * y) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                        for (int y = 0; y < 4; ++y) {
+                            const int e = e0 + 8 * y;
+                            if (e < hd) {
+                                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw4[y]);
+                                const float2 f0 = __bfloat1622float2(h2[0]), f1 = __bfloat1622float2(h2[1]);
+                                const float2 f2 = __bfloat1622float2(h2[2]), f3 = __bfloat1622float2(h2[3]);
+#pragma unroll
+                                for (int x = 0; x < 4; ++x) {
+                                    const float* qx = qs + (size_t)(h0 + x) * hd + e;
+                                    const float4 qa = *reinterpret_cast<const float4*>(qx), qb = *reinterpret_cast<const float4*>(qx + 4);
+                                    float sacc = acc[x];
+                                    sacc = fmaf(f0.x, qa.x, sacc); sacc = fmaf(f0.y, qa.y, sacc); sacc = fmaf(f1.x, qa.z, sacc); sacc = fmaf(f1.y, qa.w, sacc);
+                                    sacc = fmaf(f2.x, qb.x, sacc); sacc = fmaf(f2.y, qb.y, sacc); sacc = fmaf(f3.x, qb.z, sacc); sacc = fmaf(f3.y, qb.w, sacc);
+                                    acc[x] = sacc;
+                                }
+                            }
                         }
                     }
 #pragma unroll
@@ -424,14 +443,29 @@ ta_split_apply_kernel(const T* __restrict__ cache, const int* __restrict__ block
     const size_t v_off = (size_t)nkv * page_size * hd;
     const size_t stride = (size_t)nsplit * span;
 
-    for (int h = tid; h < nh; h += TA_THREADS) {
-        const float* st = stats + ((size_t)t * nsplit * nh + h) * 2;
-        float M = -INFINITY;
-        for (int s = 0; s < w.nvalid; ++s) M = fmaxf(M, st[(size_t)s * nh * 2]);
-        float L = 0.f;
-        for (int s = 0; s < w.nvalid; ++s) L += st[(size_t)s * nh * 2 + 1] * expf(st[(size_t)s * nh * 2] - M);
-        ms[h] = M;
-        linv[h] = 1.0f / L;
+    for (int hb = 0; hb < nh; hb += TA_THREADS / 8) {        // eight lanes per head, each a share of the ranges
+        const int h = hb + tid / 8, sub = tid & 7;
+        float M = -INFINITY, L = 0.f;
+        if (h < nh) {
+            const float* st = stats + ((size_t)t * nsplit * nh + h) * 2;
+            for (int s = sub; s < w.nvalid; s += 8) {
+                const float2 ml = *reinterpret_cast<const float2*>(st + (size_t)s * nh * 2);
+                const float m_new = fmaxf(M, ml.x);
+                L = L * expf(M - m_new) + ml.y * expf(ml.x - m_new);
+                M = m_new;
+            }
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            const float M2 = __shfl_xor_sync(0xffffffffu, M, o), L2 = __shfl_xor_sync(0xffffffffu, L, o);
+            const float m_new = fmaxf(M, M2);
+            L = (M == -INFINITY ? 0.f : L * expf(M - m_new)) + (M2 == -INFINITY ? 0.f : L2 * expf(M2 - m_new));
+            M = m_new;
+        }
+        if (h < nh && sub == 0) {
+            ms[h] = M;
+            linv[h] = 1.0f / L;
+        }
     }
     for (int i = tid; i < nh * vd; i += TA_THREADS) Os[i] = 0.f;
     if (talk)
@@ -473,15 +507,22 @@ ta_split_apply_kernel(const T* __restrict__ cache, const int* __restrict__ block
                     const float4 o4 = *reinterpret_cast<const float4*>(Os + (h0 + x) * vd + e);
                     acc[x][0] = o4.x; acc[x][1] = o4.y; acc[x][2] = o4.z; acc[x][3] = o4.w;
                 }
-                for (int jj = 0; jj < nk; ++jj) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(cache + vrow[jj] + head_off);
-                    const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-                    const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                for (int j8 = 0; j8 < nk; j8 += 8) {                // eight value pieces on their way at a time
+                    uint2 raw8[8];
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) {
-                        const float p = PM[(h0 + x) * TA_TILE + jj];
-                        acc[x][0] = fmaf(p, fa.x, acc[x][0]); acc[x][1] = fmaf(p, fa.y, acc[x][1]);
-                        acc[x][2] = fmaf(p, fb.x, acc[x][2]); acc[x][3] = fmaf(p, fb.y, acc[x][3]);
+                    for (int y = 0; y < 8; ++y)
+                        raw8[y] = j8 + y < nk ? *reinterpret_cast<const uint2*>(cache + vrow[j8 + y] + head_off) : make_uint2(0, 0);
+#pragma unroll
+                    for (int y = 0; y < 8; ++y) {
+                        const int jj = j8 + y;                          // (beyond nk: the weights of the tile's tail are zero)
+                        const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw8[y].x));
+                        const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw8[y].y));
+#pragma unroll
+                        for (int x = 0; x < 4; ++x) {
+                            const float p = PM[(h0 + x) * TA_TILE + jj];
+                            acc[x][0] = fmaf(p, fa.x, acc[x][0]); acc[x][1] = fmaf(p, fa.y, acc[x][1]);
+                            acc[x][2] = fmaf(p, fb.x, acc[x][2]); acc[x][3] = fmaf(p, fb.y, acc[x][3]);
+                        }
                     }
                 }
 #pragma unroll

@@ -251,7 +251,7 @@ def flat_pages(k_seqs, v_seqs, q_lens, page, dtype, chunk=None, seed=0, spare=3)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,vd,chunk,page", [(6, 3, 16, 24, 21, 8), (8, 2, 64, 64, 40, 16), (1, 1, 9, 7, 1, 8), (5, 5, 10, 11, None, 16),
+@pytest.mark.parametrize("H,G,d,vd,chunk,page", [(6, 3, 16, 24, 21, 8), (8, 2, 64, 32, 40, 16), (1, 1, 9, 7, 1, 8), (5, 5, 10, 11, None, 16),
                                                  (4, 1, 24, 8, 50, 8), (16, 4, 128, 64, 33, 32)])
 def test_mixed_head_attention_over_pages(K, dtype, H, G, d, vd, chunk, page):
     """Portions of prompts beside single tokens; the first tokens of a sequence; queries on both sides of a chunk's edge
@@ -277,7 +277,7 @@ def test_mixed_head_attention_over_pages(K, dtype, H, G, d, vd, chunk, page):
             at += n
 
 
-@pytest.mark.parametrize("H,G,d,vd,chunk,page", [(8, 2, 64, 64, 40, 16), (16, 4, 128, 64, 133, 32), (4, 4, 32, 128, None, 8), (16, 1, 16, 16, 64, 16),
+@pytest.mark.parametrize("H,G,d,vd,chunk,page", [(8, 2, 64, 32, 40, 16), (16, 4, 128, 64, 133, 32), (4, 4, 32, 128, None, 8), (16, 1, 16, 16, 64, 16),
                                                  (8, 8, 48, 96, 97, 16), (2, 1, 128, 128, 31, 8), (12, 6, 64, 32, 70, 16)])
 @pytest.mark.parametrize("path", ["tensor", "split", "plain"])
 def test_every_build_of_the_mixed_head_attention_gives_the_plain_result(K, H, G, d, vd, chunk, page, path):
@@ -314,7 +314,7 @@ def test_every_build_of_the_mixed_head_attention_gives_the_plain_result(K, H, G,
 def test_a_planted_key_reaches_the_tensor_core_build(K):
     """As the planted key below, in a long portion: the key at the first position of the last query's chunk takes the whole
     weight, one position lower it is not seen."""
-    H, G, d, vd, page, dtype, q_len = 8, 2, 64, 64, 16, torch.bfloat16, 200
+    H, G, d, vd, page, dtype, q_len = 8, 2, 32, 64, 16, torch.bfloat16, 200
     for chunk, ctx in ((320, 600), (250, 499), (48, 300)):
         start = ((ctx - 1) // chunk) * chunk
         v = rnd(ctx, G, vd, seed=5).to(dtype).double()
