@@ -349,12 +349,12 @@ ta_split_scores_kernel(const T* __restrict__ q, const T* __restrict__ cache, con
                 for (int j = w.k0 + lane; j < w.k1; j += 32) {
                     const T* kp = cache + (size_t)w.table[j / page_size] * page_elems + ((size_t)kvh * page_size + (j % page_size)) * hd;
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    for (int e0 = 0; e0 < hd; e0 += 32) {               // four 16-byte pieces of the row on their way at a time
-                        uint4 raw4[4];
+                    for (int e0 = 0; e0 < hd; e0 += 64) {               // eight 16-byte pieces of the row on their way at a time
+                        uint4 raw4[8];
 #pragma unroll
-                        for (int y = 0; y < 4; ++y) raw4[y] = e0 + 8 * y < hd ? *reinterpret_cast<const uint4*>(kp + e0 + 8 * y) : make_uint4(0, 0, 0, 0);
+                        for (int y = 0; y < 8; ++y) raw4[y] = e0 + 8 * y < hd ? *reinterpret_cast<const uint4*>(kp + e0 + 8 * y) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                        for (int y = 0; y < 4; ++y) {
+                        for (int y = 0; y < 8; ++y) {
                             const int e = e0 + 8 * y;
                             if (e < hd) {
                                 const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw4[y]);
