@@ -81,6 +81,7 @@ class CudaKernels:
     TALKING_SPLIT = True               # attention with mixed head weights: few tokens behind many keys go to the split-key kernels
     TALKING_SPLIT_MAX_TOKENS = 64      # ... up to this many tokens in the step
     TALKING_SPLIT_SPAN = 64            # ... in ranges of a multiple of this many keys
+    TALKING_SPLIT_MAX_SCRATCH = 512 << 20   # ... while the scores of the step fit this many bytes of scratch
     TCGEN05_ATTENTION = True           # prompt portions go to the tcgen05 attention kernel when it fits
     TCGEN05_ATTENTION_MIN_TOKENS = 16  # ... from this many tokens in the longest portion of the step
     DECODE_MAX_ROWS = 64    # rows up to which the weight-streaming tcgen05 GEMM may be used
@@ -1248,10 +1249,14 @@ class CudaKernels:
                     raise KernelError(f"talking_attention: {name} has {p.numel()} entries, expected {n}")
         out = torch.empty((T, num_heads * value_dim), dtype=q.dtype, device=q.device)
         visible = min(meta.max_ctx_len, chunk) if chunk else meta.max_ctx_len
-        if self.TALKING_SPLIT and 0 < T <= self.TALKING_SPLIT_MAX_TOKENS and visible > self.TALKING_SPLIT_SPAN \
-                and num_heads * head_dim * 4 <= 48 * 1024:
-            # few tokens behind many keys: the keys of a token are cut over CTAs (at most 64 ranges)
-            span = self.TALKING_SPLIT_SPAN * ((visible + 64 * self.TALKING_SPLIT_SPAN - 1) // (64 * self.TALKING_SPLIT_SPAN))
+        if self.TALKING_SPLIT and 0 < T and (T <= self.TALKING_SPLIT_MAX_TOKENS or meta.max_q_len == 1) \
+                and visible > self.TALKING_SPLIT_SPAN and num_heads * head_dim * 4 <= 48 * 1024 \
+                and T * num_heads * (visible + 64) * 4 <= self.TALKING_SPLIT_MAX_SCRATCH:
+            # few tokens behind many keys (or single tokens only): the keys of a token are cut over CTAs, into as many
+            # ranges as give the GPU about two CTAs an SM (at most 64), each a multiple of TALKING_SPLIT_SPAN keys
+            unit = self.TALKING_SPLIT_SPAN
+            ranges = min(64, max(1, -(-2 * self.num_sms // T)))
+            span = unit * -(-visible // (unit * ranges))
             nsplit = (visible + span - 1) // span
             lib = self._lib("talking_attention.cu")
             lib.rv_talking_attention_split_floats.restype = ctypes.c_longlong

@@ -311,6 +311,27 @@ def test_every_build_of_the_mixed_head_attention_gives_the_plain_result(K, H, G,
         K.TALKING_MMA, K.TALKING_SPLIT = old
 
 
+def test_a_large_batch_of_single_tokens_takes_the_split_keys(K):
+    """Seventy sequences of unequal lengths, one token each: more tokens than the tensor-core build is preferred from, yet
+    all of them single, so the keys are split (into fewer ranges than for a small batch); against the slow implementation."""
+    H, G, d, vd, chunk, page, dtype = 4, 2, 32, 16, 90, 16, torch.bfloat16
+    ctx = [3 + (37 * i) % 230 for i in range(70)]
+    q_lens = [1] * 70
+    ks = [rnd(c, G, d, seed=300 + i).to(dtype).double() for i, c in enumerate(ctx)]
+    vs = [rnd(c, G, vd, seed=400 + i).to(dtype).double() for i, c in enumerate(ctx)]
+    qs = [rnd(1, H, d, seed=500 + i).to(dtype).double() for i in range(70)]
+    r1, r2 = torch.rand(H, generator=torch.Generator().manual_seed(1), dtype=F64) * 1.5, torch.rand(H, generator=torch.Generator().manual_seed(2), dtype=F64) + 0.1
+    talk = torch.eye(H, dtype=F64) + 0.4 * rnd(H, H, seed=3)
+    cache, meta, positions = flat_pages(ks, vs, q_lens, page, dtype, chunk)
+    q = torch.cat(qs).reshape(70, H * d).to(dtype).cuda()
+    got = K.talking_attention(q, cache, meta, positions, H, G, d, vd, 0.3, r1.float().cuda(), r2.float().cuda(), talk.float().cuda(), chunk)
+    for i in range(70):
+        full_q = torch.zeros(ctx[i], H, d, dtype=F64)
+        full_q[-1:] = qs[i]
+        want = P.mixed_head_attention(full_q, ks[i], vs[i], 0.3, r1, r2, talk, chunk)[-1:]
+        assert rel_err(got[i:i + 1], want.reshape(1, -1)) < TOL[dtype], i
+
+
 def test_a_planted_key_reaches_the_tensor_core_build(K):
     """As the planted key below, in a long portion: the key at the first position of the last query's chunk takes the whole
     weight, one position lower it is not seen."""
