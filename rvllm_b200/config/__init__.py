@@ -3,6 +3,7 @@ from .model_config import DenseDecoderConfig, LlamaConfig, Qwen2Config, RopeScal
 from .tufirax_config import TufiraxConfig, TufiraxLayer
 from .vipelix_config import VipelixConfig, VipelixLayer
 from .tibepel_config import TibepelConfig, TibepelLayer
+from .tugodra_config import TugodraConfig, TugodraLayer
 from .registry import (register_architecture, unregister_architecture, known_architectures,
                        config_from_dict, load_config)
 from .engine_config import EngineConfig, canonical_dtype

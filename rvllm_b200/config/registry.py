@@ -13,6 +13,7 @@ from .model_config import LlamaConfig, Qwen2Config, read_config_json
 from .tufirax_config import TufiraxConfig
 from .vipelix_config import VipelixConfig
 from .tibepel_config import TibepelConfig
+from .tugodra_config import TugodraConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
 
@@ -57,3 +58,4 @@ register_architecture("Qwen2ForCausalLM", Qwen2Config)
 register_architecture("Tufirax", TufiraxConfig)
 register_architecture("Vipelix", VipelixConfig)
 register_architecture("Tibepel", TibepelConfig)
+register_architecture("Tugodra", TugodraConfig)

@@ -3,7 +3,7 @@
 //
 //   latent_prepare   rows [q: nh x (dq + dr) | c': R | r: dr | gate logits: nh] of a stacked projection.
 //                    c = c' / sqrt(mean(c'^2) + eps) * w;  the leading `rot` elements of r and of every head's last dr
-//                    query elements are turned in pairs (2i, 2i + 1) by the angle of (position, i);
+//                    query elements are turned in pairs (2i, 2i + 1) - with `halves`: (i, i + rot / 2) - by the angle of (position, i);
 //                    [c | r] goes into the token's cache slot, the unrotated query parts into q_plain [T, nh, dq],
 //                    the rotated ones into columns R .. R + dr of q_row [T, nh, R + dr] (whose leading R columns
 //                    the absorbing product fills afterwards), sigmoid of the gate logits into a float array.
@@ -30,7 +30,7 @@ latent_prepare_kernel(const void* __restrict__ proj, int in_dtype, int row_strid
                       const int* __restrict__ positions, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                       int rot, int table_rows, const int* __restrict__ slot_mapping, void* __restrict__ cache,
                       void* __restrict__ q_plain, void* __restrict__ q_row, int out_dtype, float* __restrict__ gate_out,
-                      int nh, int dq, int dr, int R, float eps, int write_kv) {
+                      int nh, int dq, int dr, int R, float eps, int write_kv, int halves) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
     __shared__ float scratch[33];
@@ -56,10 +56,11 @@ latent_prepare_kernel(const void* __restrict__ proj, int in_dtype, int row_strid
         // the shared rotated key part: pairs below `rot`, the rest as projected
         for (int i = threadIdx.x; i < dr - half; i += blockDim.x) {
             if (i < half) {
-                const float a = lt_load(proj, in_dtype, c0 + R + 2 * i), b = lt_load(proj, in_dtype, c0 + R + 2 * i + 1);
+                const int ia = halves ? i : 2 * i, ib = halves ? i + half : 2 * i + 1;         // the two elements of pair i
+                const float a = lt_load(proj, in_dtype, c0 + R + ia), b = lt_load(proj, in_dtype, c0 + R + ib);
                 const float c = cs[i], s = sn[i];
-                lt_store(cache, out_dtype, d0 + R + 2 * i, a * c - b * s);
-                lt_store(cache, out_dtype, d0 + R + 2 * i + 1, b * c + a * s);
+                lt_store(cache, out_dtype, d0 + R + ia, a * c - b * s);
+                lt_store(cache, out_dtype, d0 + R + ib, b * c + a * s);
             } else {
                 const int j = i + half;
                 lt_store(cache, out_dtype, d0 + R + j, lt_load(proj, in_dtype, c0 + R + j));
@@ -78,10 +79,11 @@ latent_prepare_kernel(const void* __restrict__ proj, int in_dtype, int row_strid
         const int k = i - dq;
         const size_t dst = ((size_t)t * nh + h) * D + R;
         if (k < half) {
-            const float a = lt_load(proj, in_dtype, src + dq + 2 * k), b = lt_load(proj, in_dtype, src + dq + 2 * k + 1);
+            const int ia = halves ? k : 2 * k, ib = halves ? k + half : 2 * k + 1;
+            const float a = lt_load(proj, in_dtype, src + dq + ia), b = lt_load(proj, in_dtype, src + dq + ib);
             const float c = cs[k], s = sn[k];
-            lt_store(q_row, out_dtype, dst + 2 * k, a * c - b * s);
-            lt_store(q_row, out_dtype, dst + 2 * k + 1, b * c + a * s);
+            lt_store(q_row, out_dtype, dst + ia, a * c - b * s);
+            lt_store(q_row, out_dtype, dst + ib, b * c + a * s);
         } else {
             const int j = k + half;
             lt_store(q_row, out_dtype, dst + j, lt_load(proj, in_dtype, src + dq + j));
@@ -97,7 +99,7 @@ latent_prepare_kernel(const void* __restrict__ proj, int in_dtype, int row_strid
 RV_EXPORT int rv_latent_prepare(const void* proj, int in_dtype, int row_stride, const void* c_gamma, int gamma_dtype,
                                 const int* positions, const float* cos_t, const float* sin_t, int rot, int table_rows,
                                 const int* slot_mapping, void* cache, void* q_plain, void* q_row, int out_dtype, float* gate_out,
-                                int n_tokens, int nh, int dq, int dr, int R, float eps, int write_kv, cudaStream_t stream) {
+                                int n_tokens, int nh, int dq, int dr, int R, float eps, int write_kv, int halves, cudaStream_t stream) {
     if (n_tokens < 0 || nh <= 0 || dq <= 0 || dr < 0 || R <= 0 || table_rows <= 0) return RV_ERR_BAD_SIZE;
     if (rot < 0 || rot > dr || (rot & 1)) return RV_ERR_BAD_SIZE;
     if (row_stride < nh * (dq + dr) + R + dr + (gate_out ? nh : 0)) return RV_ERR_BAD_SIZE;
@@ -106,7 +108,7 @@ RV_EXPORT int rv_latent_prepare(const void* proj, int in_dtype, int row_stride, 
     if (!cos_t || !sin_t) rot = 0;
     RV_LAUNCH_ST = rv_launch(latent_prepare_kernel, dim3(n_tokens), dim3(256), 0, stream, proj, in_dtype, row_stride, c_gamma,
                              gamma_dtype, positions, cos_t, sin_t, rot, table_rows, slot_mapping, cache, q_plain, q_row, out_dtype,
-                             gate_out, nh, dq, dr, R, eps, write_kv);
+                             gate_out, nh, dq, dr, R, eps, write_kv, halves);
     return rv_launch_status();
 }
 

@@ -10,6 +10,11 @@
 //   scaled_sum            a <- sa * a + sb * b (float32), or a <- sb * b where a starts
 //   act_mul_clamp         rows [gate | up] -> g sigmoid(alpha g) (u + 1), g = min(gate, L), u = clamp(up, -L, L)
 //   head_norm_gate        per head: o / sqrt(mean(o^2) + eps) * w * silu(z), w shared by the heads
+//   dynamic_tanh          tanh(alpha x) * w + b element by element (alpha: one number on the device)
+//   residual_dynamic_tanh x += tanh(alpha y) * w + b on the float32 stream and, optionally, the same form of norm of the
+//                         new x with a second (alpha, w, b), in the activations' type: the next sublayer's input
+//   scale_rows            x * s as float32 (the start of a float32 stream from a table kept in 16 bits)
+//   act_rows              relu(u)^2, optionally times one number per row, in the activations' type
 //
 // All arithmetic is float (the angle: double); storage is float or bfloat16 per argument.  Any width.
 #include "common.cuh"
@@ -212,5 +217,135 @@ RV_EXPORT int rv_head_norm_gate(const float* o, const void* gamma, int gamma_dty
     const size_t total = (size_t)rows * heads;
     RV_LAUNCH_ST = rv_launch(head_norm_gate_kernel, dim3((unsigned)((total + 7) / 8)), dim3(256), 0, stream, o, gamma, gamma_dtype, z,
                              z_dtype, z_stride, z_col0, out, out_dtype, heads, vd, eps, total);
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ Dynamic-Tanh norms
+// Element-wise, four neighbouring columns per thread where the width allows 16-byte accesses of the float arrays.
+__global__ void dynamic_tanh_kernel(const void* __restrict__ x, int x_dtype, const float* __restrict__ alpha, const float* __restrict__ w,
+                                    const float* __restrict__ b, void* __restrict__ out, int out_dtype, int cols, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const float a = alpha[0];
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % cols);
+        so_store(out, out_dtype, i, fmaf(tanhf(a * so_load(x, x_dtype, i)), w[c], b[c]));
+    }
+}
+
+// x and y float [rows, cols]; `next` (alpha2, w2, b2) optional.  vec: cols % 4 == 0 and 16-byte aligned float pointers.
+template <bool VEC>
+__global__ void residual_dynamic_tanh_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ alpha,
+                                             const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ alpha2,
+                                             const float* __restrict__ w2, const float* __restrict__ b2, void* __restrict__ out,
+                                             int out_dtype, int cols, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    const float a = alpha[0], a2 = out ? alpha2[0] : 0.f;
+    if constexpr (VEC) {
+        const size_t quads = total / 4;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+            const int c = (int)((i * 4) % cols);
+            float4 xv = reinterpret_cast<float4*>(x)[i];
+            const float4 yv = reinterpret_cast<const float4*>(y)[i];
+            const float4 wv = *reinterpret_cast<const float4*>(w + c), bv = *reinterpret_cast<const float4*>(b + c);
+            xv.x += fmaf(tanhf(a * yv.x), wv.x, bv.x); xv.y += fmaf(tanhf(a * yv.y), wv.y, bv.y);
+            xv.z += fmaf(tanhf(a * yv.z), wv.z, bv.z); xv.w += fmaf(tanhf(a * yv.w), wv.w, bv.w);
+            reinterpret_cast<float4*>(x)[i] = xv;
+            if (out) {
+                const float4 w2v = *reinterpret_cast<const float4*>(w2 + c), b2v = *reinterpret_cast<const float4*>(b2 + c);
+                const float o0 = fmaf(tanhf(a2 * xv.x), w2v.x, b2v.x), o1 = fmaf(tanhf(a2 * xv.y), w2v.y, b2v.y);
+                const float o2 = fmaf(tanhf(a2 * xv.z), w2v.z, b2v.z), o3 = fmaf(tanhf(a2 * xv.w), w2v.w, b2v.w);
+                if (out_dtype == RV_DTYPE_F32) {
+                    reinterpret_cast<float4*>(out)[i] = make_float4(o0, o1, o2, o3);
+                } else {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                    reinterpret_cast<uint2*>(out)[i] = pk;
+                }
+            }
+        }
+    } else {
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const int c = (int)(i % cols);
+            const float v = x[i] + fmaf(tanhf(a * y[i]), w[c], b[c]);
+            x[i] = v;
+            if (out) so_store(out, out_dtype, i, fmaf(tanhf(a2 * v), w2[c], b2[c]));
+        }
+    }
+}
+
+static inline int so_blocks(size_t items) {
+    const size_t want = (items + 255) / 256;
+    return (int)(want < 148 * 16 ? (want ? want : 1) : 148 * 16);
+}
+
+RV_EXPORT int rv_dynamic_tanh(const void* x, int x_dtype, const float* alpha, const float* w, const float* b, void* out, int out_dtype,
+                              int rows, int cols, cudaStream_t stream) {
+    if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
+    if ((x_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (rows == 0) return RV_OK;
+    const size_t total = (size_t)rows * cols;
+    RV_LAUNCH_ST = rv_launch(dynamic_tanh_kernel, dim3(so_blocks(total)), dim3(256), 0, stream, x, x_dtype, alpha, w, b, out, out_dtype,
+                             cols, total);
+    return rv_launch_status();
+}
+
+RV_EXPORT int rv_residual_dynamic_tanh(float* x, const float* y, const float* alpha, const float* w, const float* b, const float* alpha2,
+                                       const float* w2, const float* b2, void* out, int out_dtype, int rows, int cols,
+                                       cudaStream_t stream) {
+    if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
+    if (out_dtype & ~1) return RV_ERR_BAD_DTYPE;
+    if (out && (!alpha2 || !w2 || !b2)) return RV_ERR_BAD_SIZE;
+    if (rows == 0) return RV_OK;
+    const size_t total = (size_t)rows * cols;
+    uintptr_t bits = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(w) |
+                     reinterpret_cast<uintptr_t>(b);
+    if (out) bits |= reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(b2);
+    if (cols % 4 == 0 && bits % 16 == 0)
+        RV_LAUNCH_ST = rv_launch(residual_dynamic_tanh_kernel<true>, dim3(so_blocks(total / 4)), dim3(256), 0, stream, x, y, alpha, w, b,
+                                 alpha2, w2, b2, out, out_dtype, cols, total);
+    else
+        RV_LAUNCH_ST = rv_launch(residual_dynamic_tanh_kernel<false>, dim3(so_blocks(total)), dim3(256), 0, stream, x, y, alpha, w, b,
+                                 alpha2, w2, b2, out, out_dtype, cols, total);
+    return rv_launch_status();
+}
+
+// ------------------------------------------------------------------ scaled rows, squared-relu rows
+__global__ void scale_rows_kernel(const void* __restrict__ x, int x_dtype, float scale, float* __restrict__ out, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = so_load(x, x_dtype, i) * scale;
+}
+
+__global__ void act_rows_kernel(const void* __restrict__ u, int u_dtype, const float* __restrict__ row_scale, void* __restrict__ out,
+                                int out_dtype, int cols, size_t total) {
+    rv_pdl_launch_dependents();
+    rv_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(so_load(u, u_dtype, i), 0.f);
+        so_store(out, out_dtype, i, row_scale ? v * v * row_scale[i / cols] : v * v);
+    }
+}
+
+RV_EXPORT int rv_scale_rows(const void* x, int x_dtype, float scale, float* out, long long total, cudaStream_t stream) {
+    if (total < 0) return RV_ERR_BAD_SIZE;
+    if (x_dtype & ~1) return RV_ERR_BAD_DTYPE;
+    if (total == 0) return RV_OK;
+    RV_LAUNCH_ST = rv_launch(scale_rows_kernel, dim3(so_blocks((size_t)total)), dim3(256), 0, stream, x, x_dtype, scale, out, (size_t)total);
+    return rv_launch_status();
+}
+
+// mode 0: relu(u)^2
+RV_EXPORT int rv_act_rows(const void* u, int u_dtype, const float* row_scale, void* out, int out_dtype, int mode, int rows, int cols,
+                          cudaStream_t stream) {
+    if (rows < 0 || cols <= 0) return RV_ERR_BAD_SIZE;
+    if ((u_dtype | out_dtype) & ~1) return RV_ERR_BAD_DTYPE;
+    if (mode != 0) return RV_ERR_UNSUPPORTED;
+    if (rows == 0) return RV_OK;
+    const size_t total = (size_t)rows * cols;
+    RV_LAUNCH_ST = rv_launch(act_rows_kernel, dim3(so_blocks(total)), dim3(256), 0, stream, u, u_dtype, row_scale, out, out_dtype, cols, total);
     return rv_launch_status();
 }

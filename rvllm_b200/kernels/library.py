@@ -1289,10 +1289,11 @@ class CudaKernels:
 
     # ------------------------------------------------------------------ latent attention
     def latent_prepare(self, proj, c_gamma, eps: float, positions, cos, sin, slot_mapping, cache_layer, num_heads: int,
-                       head_dim: int, rot_dim: int, kv_rank: int, out_dtype, with_gate: bool = True, write_kv: bool = True):
+                       head_dim: int, rot_dim: int, kv_rank: int, out_dtype, with_gate: bool = True, write_kv: bool = True,
+                       halves: bool = False):
         """proj rows [q: heads x (head_dim + rot_dim) | c': kv_rank | r: rot_dim | gate logits: heads].  c' is RMS-normalised
         (weight `c_gamma`), the leading 2 * cos.shape[1] elements of r and of every head's rotated query part are turned in
-        pairs (2i, 2i + 1), [c | r] is written into the token's cache row.  Returns (q_plain [T, heads, head_dim],
+        pairs (2i, 2i + 1) - with `halves`: (i, i + cos.shape[1]) -, [c | r] is written into the token's cache row.  Returns (q_plain [T, heads, head_dim],
         q_row [T, heads, kv_rank + rot_dim] with its last rot_dim columns filled, sigmoid(gate logits) float [T, heads] or None)."""
         _need(proj, "proj", dims=2); _need(positions, "positions", torch.int32, 1); _need(c_gamma, "c_gamma", dims=1)
         T, row = proj.shape[0], kv_rank + rot_dim
@@ -1316,7 +1317,8 @@ class CudaKernels:
             _ptr(proj), c_int(self._dt(proj, "proj")), c_int(proj.shape[1]), _ptr(c_gamma), c_int(self._dt(c_gamma, "c_gamma")),
             _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot), c_int(table_rows), _ptr(slot_mapping if write_kv else None),
             _ptr(cache_layer if write_kv else None), _ptr(q_plain), _ptr(q_row), c_int(_DT[out_dtype]), _ptr(gate), c_int(T),
-            c_int(num_heads), c_int(head_dim), c_int(rot_dim), c_int(kv_rank), c_float(eps), c_int(1 if write_kv else 0), self._stream())
+            c_int(num_heads), c_int(head_dim), c_int(rot_dim), c_int(kv_rank), c_float(eps), c_int(1 if write_kv else 0),
+            c_int(1 if halves else 0), self._stream())
         _check("latent_prepare", st)
         return q_plain, q_row, gate
 
@@ -1387,11 +1389,11 @@ class CudaKernels:
         return True
 
     def latent_attention(self, q_row, cache_layer, meta: AttentionMeta, num_heads: int, row: int, value_dim: int, scale: float,
-                         gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         gate: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention of the step's tokens over cached rows that are key and value at once: every head's query
         [T, heads, row] meets the whole row of a token, the weighted sum is taken over the rows' leading `value_dim`
-        elements.  Causal, softmax in float; `gate` (float [T, heads]) multiplies each head's result.  Returns
-        [T, heads, value_dim] in q's type."""
+        elements.  Causal, softmax in float; `gate` (float [T, heads]) multiplies each head's result; `sinks` (float [heads]):
+        exp(sink) joins each head's softmax denominator.  Returns [T, heads, value_dim] in q's type."""
         _need(q_row, "q_row", dims=3); _need(cache_layer, "cache_layer", q_row.dtype, 5)
         T = q_row.shape[0]
         if q_row.shape[1] != num_heads or q_row.shape[2] != row or tuple(cache_layer.shape[1:3]) != (1, 1) or cache_layer.shape[4] != row:
@@ -1399,7 +1401,7 @@ class CudaKernels:
                               f"{num_heads} heads on rows of {row}")
         if not 0 < value_dim <= row:
             raise KernelError(f"latent_attention: a value of {value_dim} out of a row of {row}")
-        self._check_attention_extras(q_row.view(T, -1), num_heads, None, gate)
+        self._check_attention_extras(q_row.view(T, -1), num_heads, sinks, gate)
         out = torch.empty((T, num_heads, value_dim), dtype=q_row.dtype, device=q_row.device)
         page = cache_layer.shape[3]
         flash_ok = (self.LATENT_FLASH and q_row.dtype == torch.bfloat16 and row % 16 == 0 and value_dim % 16 == 0 and row <= 256
@@ -1409,41 +1411,50 @@ class CudaKernels:
                 and meta.max_q_len >= self.TCGEN05_ATTENTION_MIN_TOKENS and (flash_ok or meta.num_decode == 0)):
             # prompt portions on the tcgen05 kernel (all heads of a token side by side in a tile of 128 rows); the step's
             # one-token sequences, which it leaves alone, on the decode tiling of the mma.sync kernel
-            self.attention_tcgen05(q_row, cache_layer, meta, out, num_heads, 1, row, scale, None, gate=gate, value_dim=value_dim)
+            self.attention_tcgen05(q_row, cache_layer, meta, out, num_heads, 1, row, scale, None, gate=gate, sinks=sinks, value_dim=value_dim)
             if meta.num_decode:
                 self.flash_attention(q_row, cache_layer, meta, out, num_heads, 1, row, scale, None, mode=1, q_filter=1, max_q_len=1,
-                                     gate=gate, value_dim=value_dim)
+                                     gate=gate, sinks=sinks, value_dim=value_dim)
             return out
         if flash_ok:
             # the tensor-core kernel: all heads of a token are rows of one tile over the token's single "kv head"
             args = (q_row, cache_layer, meta, out, num_heads, 1, row, scale, None)
             if meta.max_q_len == 1:
-                self.flash_attention(*args, mode=1, num_splits=self.decode_splits(meta, num_heads, 1), gate=gate, value_dim=value_dim)
+                self.flash_attention(*args, mode=1, num_splits=self.decode_splits(meta, num_heads, 1), gate=gate, sinks=sinks, value_dim=value_dim)
             elif meta.num_decode == 0:
-                self.flash_attention(*args, mode=0, gate=gate, value_dim=value_dim)
+                self.flash_attention(*args, mode=0, gate=gate, sinks=sinks, value_dim=value_dim)
             else:
-                self.flash_attention(*args, mode=0, q_filter=2, gate=gate, value_dim=value_dim)
-                self.flash_attention(*args, mode=1, q_filter=1, max_q_len=1, gate=gate, value_dim=value_dim)
+                self.flash_attention(*args, mode=0, q_filter=2, gate=gate, sinks=sinks, value_dim=value_dim)
+                self.flash_attention(*args, mode=1, q_filter=1, max_q_len=1, gate=gate, sinks=sinks, value_dim=value_dim)
             return out
         st = self._lib("attention_ref.cu").rv_paged_attention_ref_ex(
             _ptr(q_row), _ptr(cache_layer), _ptr(meta.block_tables), _ptr(meta.cu_seqlens), _ptr(meta.ctx_lens),
             _ptr(meta.token_seq), _ptr(out), c_int(T), c_int(num_heads), c_int(1), c_int(row), c_int(cache_layer.shape[3]),
-            c_int(meta.max_blocks), c_float(scale), c_int(0), c_float(0.0), _ptr(None), _ptr(gate), c_int(1), c_int(value_dim),
+            c_int(meta.max_blocks), c_float(scale), c_int(0), c_float(0.0), _ptr(sinks), _ptr(gate), c_int(1), c_int(value_dim),
             c_int(self._dt(q_row, "q_row")), self._stream())
         _check("latent_attention", st)
         return out
 
     # ------------------------------------------------------------------ mixture of experts
-    def moe_experts(self, x, chosen, gate_up, down, weight: float, add: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
-        """out[t] = (add[t]) + weight * sum_k down[e] (silu(gate[e] x_t) * (up[e] x_t)), e = chosen[t, k].
-        gate_up [experts, 2 ff, width] (gate rows, then up rows), down [experts, width, ff], chosen int32 [T, top],
-        add float32 [T, width] or None."""
+    def moe_experts(self, x, chosen, gate_up, down, weight: float, add: Optional[torch.Tensor] = None, out_dtype=None,
+                    weights: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+        """out[t] = (add[t]) + weight * sum_k weights[t, k] down[e] a_e(x_t), e = chosen[t, k].
+        activation "silu": gated experts, a_e(x) = silu(gate[e] x) * (up[e] x), gate_up [experts, 2 ff, width] (gate rows, then up
+        rows); "relu2": plain experts, a_e(x) = relu(up[e] x)^2, `gate_up` is up [experts, ff, width].  down [experts, width, ff],
+        chosen int32 [T, top], weights float32 [T, top] or None (all 1), add float32 [T, width] or None."""
         _need(x, "x", dims=2); _need(chosen, "chosen", torch.int32, 2)
         _need(gate_up, "gate_up", x.dtype, 3); _need(down, "down", x.dtype, 3)
+        if activation not in ("silu", "relu2"):
+            raise KernelError(f"moe_experts: activation {activation!r} is not known (silu, relu2)")
+        gated = activation == "silu"
         T, width = x.shape
         E, ff2, _ = gate_up.shape
-        ff, top = ff2 // 2, chosen.shape[1]
-        if gate_up.shape[2] != width or tuple(down.shape) != (E, width, ff) or chosen.shape[0] != T or ff * 2 != ff2:
+        ff, top = (ff2 // 2 if gated else ff2), chosen.shape[1]
+        if weights is not None:
+            _need(weights, "weights", torch.float32, 2)
+            if weights.shape != chosen.shape:
+                raise KernelError(f"moe_experts: weights {tuple(weights.shape)} against chosen {tuple(chosen.shape)}")
+        if gate_up.shape[2] != width or tuple(down.shape) != (E, width, ff) or chosen.shape[0] != T or (gated and ff * 2 != ff2):
             raise KernelError(f"moe_experts: x {tuple(x.shape)}, gate_up {tuple(gate_up.shape)}, down {tuple(down.shape)}, "
                               f"chosen {tuple(chosen.shape)} do not fit together")
         if add is not None:
@@ -1454,12 +1465,13 @@ class CudaKernels:
         if out_dtype not in (x.dtype, torch.float32):
             raise KernelError(f"moe_experts: result type {out_dtype} for operands of {x.dtype}")
         if x.dtype == torch.bfloat16 and T >= self.MOE_GROUPED_MIN_TOKENS and width % 8 == 0 and ff % 8 == 0 and E <= 4096:
-            return self._moe_grouped(x, chosen, gate_up, down, weight, add, out_dtype)
+            return self._moe_grouped(x, chosen, gate_up, down, weight, add, out_dtype, weights, gated)
         act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
         out = torch.empty((T, width), dtype=out_dtype, device=x.device)
-        st = self._lib("moe.cu").rv_moe_experts(
-            _ptr(x), _ptr(chosen), _ptr(gate_up), _ptr(down), _ptr(act), _ptr(add), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
-            c_int(T), c_int(top), c_int(E), c_int(ff), c_int(width), c_float(weight), c_int(self._dt(x, "x")), self._stream())
+        st = self._lib("moe.cu").rv_moe_experts_ex(
+            _ptr(x), _ptr(chosen), _ptr(weights), _ptr(gate_up), _ptr(down), _ptr(act), _ptr(add), _ptr(out),
+            c_int(1 if out_dtype == torch.float32 else 0), c_int(T), c_int(top), c_int(E), c_int(ff), c_int(width), c_float(weight),
+            c_int(1 if gated else 0), c_int(self._dt(x, "x")), self._stream())
         _check("moe_experts", st)
         COUNTERS['launches'] += 1
         return out
@@ -1467,14 +1479,16 @@ class CudaKernels:
     MOE_GROUPED_MIN_TOKENS = 128      # tokens of a step from which the experts' products run grouped on the tcgen05 GEMM ...
     MOE_GROUPED_PAIRS = True          # ... on pairs of CTAs (cta_group::2): two blocks of 128 rows of one expert share every tile of its weights
 
-    def _moe_grouped(self, x, chosen, gate_up, down, weight, add, out_dtype):
+    def _moe_grouped(self, x, chosen, gate_up, down, weight, add, out_dtype, weights=None, gated=True):
         """`moe_experts` for many bfloat16 tokens: the (token, slot) pairs sorted by expert, every expert's rows padded to
-        whole blocks of 128, two grouped tcgen05 products over the sorted rows (gate/up with the SiLU epilogue, then down with a
-        float32 result), and the weighted sum per token.  Everything is decided on the device; the buffers are sized for
-        the worst case (every expert's last block nearly empty)."""
+        whole blocks of 128, two grouped tcgen05 products over the sorted rows (gate/up with the SiLU epilogue - plain experts:
+        up with a float32 result and the squared relu in a kernel of its own - then down with a float32 result), and the
+        weighted sum per token.  Everything is decided on the device; the buffers are sized for the worst case (every
+        expert's last block nearly empty)."""
         T, width = x.shape
         E, ff2, _ = gate_up.shape
-        ff, top = ff2 // 2, chosen.shape[1]
+        ff, top = (ff2 // 2 if gated else ff2), chosen.shape[1]
+        epi = 2 if gated else 0
         lib = self._lib("gemm_tcgen05.cu", ("-DRV_PAIR=1",) if self.MOE_GROUPED_PAIRS else ())
         moe = self._lib("moe.cu")
         R, ranks = int(lib.rv_gemm_tcgen05_block_rows()), int(lib.rv_gemm_tcgen05_ranks())
@@ -1487,7 +1501,7 @@ class CudaKernels:
         src_of = torch.empty((rows,), dtype=torch.int32, device=dev)
         tile_group = torch.empty((units,), dtype=torch.int32, device=dev)
         tile_rows = torch.empty((units * ranks,), dtype=torch.int32, device=dev)
-        nt_a, nt_b = int(lib.rv_gemm_tcgen05_column_tiles(c_int(ff2), c_int(2))), int(lib.rv_gemm_tcgen05_column_tiles(c_int(width), c_int(0)))
+        nt_a, nt_b = int(lib.rv_gemm_tcgen05_column_tiles(c_int(ff2), c_int(epi))), int(lib.rv_gemm_tcgen05_column_tiles(c_int(width), c_int(0)))
         order_a = torch.empty((units * nt_a,), dtype=torch.int32, device=dev)
         order_b = torch.empty((units * nt_b,), dtype=torch.int32, device=dev)
         _check("moe_route", moe.rv_moe_route(_ptr(chosen), c_int(pairs), c_int(top), c_int(E), c_int(R), c_int(rows), c_int(ranks),
@@ -1495,17 +1509,171 @@ class CudaKernels:
                                              _ptr(order_a), c_int(nt_b), _ptr(order_b), self._stream()))
         xs = torch.empty((rows, width), dtype=torch.bfloat16, device=dev)
         _check("moe_gather", moe.rv_moe_gather(_ptr(x), _ptr(src_of), _ptr(xs), c_int(rows), c_int(width * 2), self._stream()))
-        act = torch.empty((rows, ff), dtype=torch.bfloat16, device=dev)
+        act = torch.empty((rows, ff), dtype=torch.bfloat16 if gated else torch.float32, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
-            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(order_a), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E),
-            c_int(units), c_int(2), _ptr(self._status), self._stream()))
+            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(order_a), _ptr(act), c_int(0 if gated else 1), c_int(rows), c_int(ff2), c_int(width), c_int(E),
+            c_int(units), c_int(epi), _ptr(self._status), self._stream()))
+        if not gated:
+            act = self.act_rows(act, "relu2", torch.bfloat16)
         ys = torch.empty((rows, width), dtype=torch.float32, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
             _ptr(act), _ptr(down), _ptr(tile_group), _ptr(tile_rows), _ptr(order_b), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E),
             c_int(units), c_int(0), _ptr(self._status), self._stream()))
         out = torch.empty((T, width), dtype=out_dtype, device=dev)
         _check("moe_combine", moe.rv_moe_combine(_ptr(ys), _ptr(row_of), _ptr(add), _ptr(out), c_int(1 if out_dtype == torch.float32 else 0),
-                                                 c_int(T), c_int(top), c_int(width), c_float(weight), self._stream()))
+                                                 c_int(T), c_int(top), c_int(width), c_float(weight), _ptr(weights), self._stream()))
+        return out
+
+    def moe_route_top(self, scores, correction, experts: int, top: int, groups: int, keep: int, weight_eps: float,
+                      shared_gate: bool = False):
+        """A router's choice from its float32 logits [T, experts (+ 1)]: s = sigmoid(logits); the `top` experts with the largest
+        s + correction among those of the `keep` best of `groups` equal groups of neighbouring experts (a group counts by the
+        sum of its two largest corrected scores).  Returns (chosen int32 [T, top], weights float32 [T, top] = the chosen s over
+        their sum + weight_eps, sigmoid of the last column float32 [T] with `shared_gate`, else None)."""
+        _need(scores, "scores", torch.float32, 2); _need(correction, "correction", torch.float32, 1)
+        T = scores.shape[0]
+        if scores.shape[1] != experts + (1 if shared_gate else 0) or correction.shape[0] != experts:
+            raise KernelError(f"moe_route_top: logits {tuple(scores.shape)} and {correction.shape[0]} corrections for {experts} experts")
+        chosen = torch.empty((T, top), dtype=torch.int32, device=scores.device)
+        weights = torch.empty((T, top), dtype=torch.float32, device=scores.device)
+        gate = torch.empty((T,), dtype=torch.float32, device=scores.device) if shared_gate else None
+        st = self._lib("moe.cu").rv_moe_route_top(
+            _ptr(scores), c_int(scores.shape[1]), _ptr(correction), _ptr(chosen), _ptr(weights), _ptr(gate), c_int(T), c_int(experts),
+            c_int(top), c_int(groups), c_int(keep), c_float(weight_eps), self._stream())
+        _check("moe_route_top", st)
+        return chosen, weights, gate
+
+    # ------------------------------------------------------------------ Dynamic-Tanh norms and rows
+    def dynamic_tanh(self, x, alpha, weight, bias, out_dtype=None) -> torch.Tensor:
+        """tanh(alpha x) * weight + bias; alpha float32 [1] on the device, weight and bias float32 [cols]."""
+        _need(x, "x", dims=2); _need(alpha, "alpha", torch.float32, 1)
+        _need(weight, "weight", torch.float32, 1); _need(bias, "bias", torch.float32, 1)
+        rows, cols = x.shape
+        if weight.shape[0] != cols or bias.shape[0] != cols or alpha.shape[0] != 1:
+            raise KernelError(f"dynamic_tanh: weight {tuple(weight.shape)}, bias {tuple(bias.shape)}, alpha {tuple(alpha.shape)} for rows of {cols}")
+        out = torch.empty((rows, cols), dtype=out_dtype or x.dtype, device=x.device)
+        st = self._lib("streamops.cu").rv_dynamic_tanh(_ptr(x), c_int(self._dt(x, "x")), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out),
+                                                       c_int(self._dt(out, "out")), c_int(rows), c_int(cols), self._stream())
+        _check("dynamic_tanh", st)
+        return out
+
+    def residual_dynamic_tanh(self, y, norm, x, next_norm, out_dtype):
+        """x += tanh(alpha y) * w + b on the float32 stream, in place; norm = (alpha [1], w, b).  With `next_norm` of the same
+        form the second result is that norm of the new x in `out_dtype`.  Returns (x, second result or None)."""
+        _need(x, "x", torch.float32, 2); _need(y, "y", torch.float32, 2)
+        if y.shape != x.shape:
+            raise KernelError(f"residual_dynamic_tanh: {tuple(y.shape)} added to {tuple(x.shape)}")
+        rows, cols = x.shape
+        for n in (norm, next_norm):
+            if n is not None:
+                _need(n[0], "alpha", torch.float32, 1); _need(n[1], "weight", torch.float32, 1); _need(n[2], "bias", torch.float32, 1)
+                if n[0].shape[0] != 1 or n[1].shape[0] != cols or n[2].shape[0] != cols:
+                    raise KernelError(f"residual_dynamic_tanh: a norm of {n[1].shape[0]} weights for rows of {cols}")
+        out = torch.empty((rows, cols), dtype=out_dtype, device=x.device) if next_norm is not None else None
+        a2, w2, b2 = next_norm if next_norm is not None else (None, None, None)
+        st = self._lib("streamops.cu").rv_residual_dynamic_tanh(
+            _ptr(x), _ptr(y), _ptr(norm[0]), _ptr(norm[1]), _ptr(norm[2]), _ptr(a2), _ptr(w2), _ptr(b2), _ptr(out),
+            c_int(_DT[out_dtype] if out is not None else 0), c_int(rows), c_int(cols), self._stream())
+        _check("residual_dynamic_tanh", st)
+        return x, out
+
+    def scale_rows(self, x, scale: float) -> torch.Tensor:
+        """x * scale as a new float32 tensor."""
+        _need(x, "x")
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        st = self._lib("streamops.cu").rv_scale_rows(_ptr(x), c_int(self._dt(x, "x")), c_float(scale), _ptr(out),
+                                                     ctypes.c_longlong(x.numel()), self._stream())
+        _check("scale_rows", st)
+        return out
+
+    def act_rows(self, u, activation: str, out_dtype, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """relu(u)^2 ("relu2"), times row_scale[t] (float32 [rows]) where given, in `out_dtype`."""
+        _need(u, "u", dims=2)
+        if activation != "relu2":
+            raise KernelError(f"act_rows: activation {activation!r} is not known (relu2)")
+        rows, cols = u.shape
+        if row_scale is not None:
+            _need(row_scale, "row_scale", torch.float32, 1)
+            if row_scale.shape[0] != rows:
+                raise KernelError(f"act_rows: {row_scale.shape[0]} row scales for {rows} rows")
+        out = torch.empty((rows, cols), dtype=out_dtype, device=u.device)
+        st = self._lib("streamops.cu").rv_act_rows(_ptr(u), c_int(self._dt(u, "u")), _ptr(row_scale), _ptr(out), c_int(_DT[out_dtype]),
+                                                   c_int(0), c_int(rows), c_int(cols), self._stream())
+        _check("act_rows", st)
+        return out
+
+    # ------------------------------------------------------------------ unit-norm attention, mLSTM
+    def qk_unit_prepare(self, proj, eps: float, positions, cos, sin, slot_mapping, cache_layer, num_heads: int, num_kv_heads: int,
+                        head_dim: int, value_dim: int, slot_dim: int, out_dtype, halves: bool = False, with_gate: bool = True,
+                        write_kv: bool = True):
+        """proj float32 rows [q: heads x head_dim | k: kv heads x head_dim | v: kv heads x value_dim | gate logits: heads] (k and v
+        only with `write_kv`).  q and k: the leading 2 * cos.shape[1] elements of every head turn in pairs (2i, 2i + 1) - with
+        `halves`: (i, i + cos.shape[1]) -, then the head is divided by sqrt(mean(x^2) + eps).  k and v go into the token's
+        cache slot, in heads of `slot_dim` elements whose tail is zeros.  Returns (q [T, heads * slot_dim] in `out_dtype`,
+        sigmoid(gate logits) float32 [T, heads] or None)."""
+        _need(proj, "proj", torch.float32, 2); _need(positions, "positions", torch.int32, 1)
+        T = proj.shape[0]
+        want = num_heads * head_dim + (num_kv_heads * (head_dim + value_dim) if write_kv else 0) + (num_heads if with_gate else 0)
+        if proj.shape[1] != want or slot_dim < max(head_dim, value_dim):
+            raise KernelError(f"qk_unit_prepare: rows of {proj.shape[1]} columns do not fit {num_heads} heads of {head_dim}"
+                              + (f", {num_kv_heads} key/value heads of {head_dim} / {value_dim}" if write_kv else "")
+                              + (f" and {num_heads} gates" if with_gate else "") + f" in slots of {slot_dim}")
+        rot, table_rows = 0, 1
+        if cos is not None:
+            _need(cos, "cos", torch.float32, 2); _need(sin, "sin", torch.float32, 2)
+            rot, table_rows = 2 * cos.shape[1], cos.shape[0]
+            if not 0 < rot <= head_dim or sin.shape != cos.shape:
+                raise KernelError(f"qk_unit_prepare: cos/sin tables must be [rows, dims/2] with dims <= {head_dim}")
+        page = 1
+        if write_kv:
+            _need(cache_layer, "cache_layer", out_dtype, 5); _need(slot_mapping, "slot_mapping", torch.int32, 1)
+            if cache_layer.shape[1] != 2 or cache_layer.shape[2] != num_kv_heads or cache_layer.shape[4] != slot_dim:
+                raise KernelError(f"qk_unit_prepare: cache layer of shape {tuple(cache_layer.shape)} for {num_kv_heads} heads of {slot_dim}")
+            page = cache_layer.shape[3]
+        q = torch.empty((T, num_heads * slot_dim), dtype=out_dtype, device=proj.device)
+        gate = torch.empty((T, num_heads), dtype=torch.float32, device=proj.device) if with_gate else None
+        st = self._lib("qk_prepare.cu").rv_qk_unit_prepare(
+            _ptr(proj), c_int(proj.shape[1]), _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot), c_int(table_rows),
+            c_int(1 if halves else 0), _ptr(slot_mapping if write_kv else None), _ptr(cache_layer if write_kv else None), _ptr(q),
+            c_int(_DT[out_dtype]), _ptr(gate), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(value_dim),
+            c_int(slot_dim), c_int(page), c_float(eps), c_int(1 if write_kv else 0), self._stream())
+        _check("qk_unit_prepare", st)
+        return q, gate
+
+    def mlstm_scan(self, proj, i_col0: int, f_col0: int, i_bias, f_bias, cu_seqlens, state_slots, state, heads: int, head_dim: int,
+                   value_dim: int, cap: float):
+        """The mLSTM recurrence over the step's tokens, per sequence from the memory its state row holds ([heads][head_dim]
+        [value_dim + 1] floats; the last column of a head is the normaliser) and back into it.  proj float32 rows
+        [q | k | v | ...] with the raw input- and forget-gate columns at i_col0 and f_col0.  Returns (raw float32
+        [T, heads * (value_dim + 1)]: per head the numerators S^T q and, last, n . q; top float32 [T, heads]: the running
+        maximum m_t).  The m of the state row is left as it was: `mlstm_output` stores the new one."""
+        _need(proj, "proj", torch.float32, 2); _need(state, "state", torch.float32, 2)
+        _need(i_bias, "i_bias", torch.float32, 1); _need(f_bias, "f_bias", torch.float32, 1)
+        T = proj.shape[0]
+        raw = torch.empty((T, heads * (value_dim + 1)), dtype=torch.float32, device=proj.device)
+        top = torch.empty((T, heads), dtype=torch.float32, device=proj.device)
+        st = self._lib("mlstm.cu").rv_mlstm_scan(
+            _ptr(proj), c_int(proj.shape[1]), c_int(i_col0), c_int(f_col0), _ptr(i_bias), _ptr(f_bias), _ptr(cu_seqlens), _ptr(state_slots),
+            _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(raw), _ptr(top), c_int(cu_seqlens.shape[0] - 1), c_int(heads),
+            c_int(head_dim), c_int(value_dim), c_float(cap), self._stream())
+        _check("mlstm_scan", st)
+        return raw, top
+
+    def mlstm_output(self, raw, top, gamma, eps: float, den_eps: float, proj, g_col0: int, heads: int, head_dim: int, value_dim: int,
+                     out_dtype, token_seq, cu_seqlens, state_slots, state) -> torch.Tensor:
+        """o = numerators / (max(|n . q|, exp(-m)) + den_eps); per head o / sqrt(mean(o^2) + eps) * gamma * sigmoid(gate columns
+        of proj from g_col0 on), in `out_dtype`; and the m of every sequence's last token into its state row."""
+        _need(raw, "raw", torch.float32, 2); _need(top, "top", torch.float32, 2); _need(gamma, "gamma", torch.float32, 1)
+        _need(proj, "proj", torch.float32, 2); _need(state, "state", torch.float32, 2)
+        T = raw.shape[0]
+        if raw.shape[1] != heads * (value_dim + 1) or tuple(top.shape) != (T, heads) or gamma.shape[0] != heads * value_dim:
+            raise KernelError(f"mlstm_output: raw {tuple(raw.shape)}, top {tuple(top.shape)}, gamma {tuple(gamma.shape)} for {heads} heads of {value_dim}")
+        out = torch.empty((T, heads * value_dim), dtype=out_dtype, device=raw.device)
+        st = self._lib("mlstm.cu").rv_mlstm_output(
+            _ptr(raw), _ptr(top), _ptr(gamma), _ptr(proj), c_int(proj.shape[1]), c_int(g_col0), _ptr(out), c_int(_DT[out_dtype]), c_int(T),
+            c_int(heads), c_int(head_dim), c_int(value_dim), c_float(eps), c_float(den_eps), _ptr(token_seq), _ptr(cu_seqlens),
+            _ptr(state_slots), _ptr(state), ctypes.c_longlong(state.stride(0)), self._stream())
+        _check("mlstm_output", st)
         return out
 
     # ------------------------------------------------------------------ sampling

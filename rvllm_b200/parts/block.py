@@ -104,11 +104,13 @@ BLOCKS.register("output_norm_residual", OutputNormResidualBlock)
 
 class SandwichNormResidualBlock:
     """`sandwich_norm_residual`: x + norm_out(mixer(norm_in(x))), then x + norm_out'(feed_forward(norm_in'(x))): every
-    sublayer has an RMSNorm in front of it and one on what it returns.  A layer may have no feed-forward.
+    sublayer has a norm in front of it and one on what it returns.  A layer may have no feed-forward.  The norms of a layer
+    are all RMSNorms (`as_rms()`) or all Dynamic-Tanh norms (`as_dyt()`).
 
     The stream x is float32 whatever the engine's type (`ModelSpec.residual_dtype`); sublayers are asked for a float32
     result, which is normalised and added in 32 bits.  One kernel does the sum and the norm in front of the NEXT sublayer
-    of the layer (two row statistics in one pass over the row), and leaves that sublayer's input in the activations' type."""
+    of the layer (for RMSNorms two row statistics in one pass over the row), and leaves that sublayer's input in the
+    activations' type."""
     ROLES = ("mixer", "mixer_norm", "mixer_out_norm")
     OPTIONAL = ("feed_forward", "feed_forward_norm", "feed_forward_out_norm")
 
@@ -121,22 +123,40 @@ class SandwichNormResidualBlock:
                               f"{', '.join(self.OPTIONAL)}; got {', '.join(sorted(parts))}")
         self.mixer, self.mixer_norm, self.mixer_out_norm = (parts[r] for r in self.ROLES)
         self.feed_forward, self.feed_forward_norm, self.feed_forward_out_norm = (parts.get(r) for r in self.OPTIONAL)
-        for n in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm):
-            if n is not None and not hasattr(n, "as_rms"):
-                raise ConfigError("the sandwich-norm residual block needs norms that offer `as_rms()` (an RMSNorm)")
+        norms = [n for n in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm) if n is not None]
+        if all(hasattr(n, "as_rms") for n in norms):
+            self.kind = "rms"
+        elif all(hasattr(n, "as_dyt") for n in norms):
+            self.kind = "dyt"
+        else:
+            raise ConfigError("the sandwich-norm residual block needs norms that all offer `as_rms()` (RMSNorm) or all "
+                              "`as_dyt()` (Dynamic Tanh)")
+
+    def _norm(self, k, norm, x, dtype):
+        if self.kind == "rms":
+            return k.rmsnorm(x, *norm.as_rms(), out_dtype=dtype)
+        return k.dynamic_tanh(x, *norm.as_dyt(), out_dtype=dtype)
+
+    def _add(self, k, norm, y, x, dtype, next_norm):
+        """x + norm(y) and, with `next_norm`, that norm of the sum in `dtype`."""
+        if self.kind == "rms":
+            if next_norm is None:
+                return k.residual_rmsnorm(y, *norm.as_rms(), x, None)[0], None
+            return k.residual_rmsnorm(y, *norm.as_rms(), x, dtype, next_norm=next_norm.as_rms())
+        return k.residual_dynamic_tanh(y, norm.as_dyt(), x, None if next_norm is None else next_norm.as_dyt(), dtype)
 
     def __call__(self, x, ctx, cache, write_cache=True):
         k = ctx.kernels
         dtype = ctx.extras.get("activation_dtype", x.dtype)
         if x.dtype != torch.float32:
             x = x.float()
-        h = k.rmsnorm(x, *self.mixer_norm.as_rms(), out_dtype=dtype)
+        h = self._norm(k, self.mixer_norm, x, dtype)
         y = self.mixer(h, ctx, cache, residual=None, write_cache=write_cache, out_dtype=torch.float32)
         if self.feed_forward is None:
-            return k.residual_rmsnorm(y, *self.mixer_out_norm.as_rms(), x, None)[0]
-        x, h = k.residual_rmsnorm(y, *self.mixer_out_norm.as_rms(), x, dtype, next_norm=self.feed_forward_norm.as_rms())
+            return self._add(k, self.mixer_out_norm, y, x, dtype, None)[0]
+        x, h = self._add(k, self.mixer_out_norm, y, x, dtype, self.feed_forward_norm)
         y = self.feed_forward(h, ctx, residual=None, out_dtype=torch.float32)
-        return k.residual_rmsnorm(y, *self.feed_forward_out_norm.as_rms(), x, None)[0]
+        return self._add(k, self.feed_forward_out_norm, y, x, dtype, None)[0]
 
 
 BLOCKS.register("sandwich_norm_residual", SandwichNormResidualBlock)

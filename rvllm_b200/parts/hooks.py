@@ -5,6 +5,7 @@
                   tensor [rows, width] of the checkpoint named in full (several entries share it, each with its row).
                   This is what a model that runs a span of its layers several times adds at the start of each pass:
                   the embedded tokens again, and a vector that tells the passes apart.  The sum is float32.
+`embedding_scale` on the embedded tokens: x <- scale * x, formed in float32 (the start of a float32 residual stream).
 """
 from __future__ import annotations
 
@@ -46,5 +47,14 @@ class StreamOffset(Part):
         return ctx.kernels.stream_add(x, emb, self.table, self.index)
 
 
+class EmbeddingScale(Part):
+    def __init__(self, scale: float):
+        self.scale = float(scale)
+
+    def __call__(self, x, ctx):
+        return ctx.kernels.scale_rows(x, self.scale)
+
+
+HOOKS.register("embedding_scale", EmbeddingScale)
 HOOKS.register("logit_softcap", LogitSoftcap)
 HOOKS.register("stream_offset", StreamOffset)

@@ -1,4 +1,6 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * gamma, arithmetic in float; gamma is the stored weight, or one plus
+"""Norms of a layer.
+
+RMSNorm: y = x / sqrt(mean(x^2) + eps) * gamma, arithmetic in float; gamma is the stored weight, or one plus
 the stored weight for checkpoints that keep it around zero (`unit_offset`).
 
 v3/crates/rvllm-fused/src/reference.rs:12-24 and kernels/fused_rmsnorm_fp8_quant.cu:61-84 of
@@ -36,3 +38,31 @@ class RMSNorm(Part):
 
 
 NORMS.register("rmsnorm", RMSNorm)
+
+
+class DynamicTanh(Part):
+    """y = tanh(alpha x) * weight + bias, element by element: a norm that forms no statistic of the row.  `alpha` is one
+    number, stored beside the weight as `<tensor>.alpha`; the bias as `<tensor>.b`.  Arithmetic in float32; the three
+    tensors are kept in float32 whatever the engine's type."""
+
+    def __init__(self, size: int, tensor: str = "weight", bias_suffix: str = ".b", alpha_suffix: str = ".alpha"):
+        self.size, self.tensor, self.bias_name, self.alpha_name = size, tensor, tensor + bias_suffix, tensor + alpha_suffix
+        self.weight = self.bias = self.alpha = None
+
+    def tensor_specs(self):
+        return {self.tensor: TensorSpec((self.size,), "norm"), self.bias_name: TensorSpec((self.size,), "bias"),
+                self.alpha_name: TensorSpec((), "unit_scale")}
+
+    def bind(self, get):
+        self.weight, self.bias = get(self.tensor).float().contiguous(), get(self.bias_name).float().contiguous()
+        self.alpha = get(self.alpha_name).float().reshape(1).contiguous()
+
+    def __call__(self, x, ctx):
+        return ctx.kernels.dynamic_tanh(x, *self.as_dyt(), out_dtype=ctx.extras.get("activation_dtype", x.dtype))
+
+    def as_dyt(self):
+        """(alpha [1], weight, bias), float32, for a block that applies this norm inside a fused kernel."""
+        return self.alpha, self.weight, self.bias
+
+
+NORMS.register("dynamic_tanh", DynamicTanh)

@@ -3,7 +3,7 @@ configuration and a seed.
 
 Distributions: matrices N(0, 0.02), norm weights 1 + N(0, 0.1), biases N(0, 0.02), taps of a
 short convolution N(0, 0.3), coefficients of an activation 0.5 + N(0, 0.3), a matrix that
-mixes heads N(0, 0.3); an init kind "choice:E" is an
+mixes heads N(0, 0.3), the scalar of a Dynamic-Tanh norm 0.7 + N(0, 0.1); an init kind "choice:E" is an
 integer table whose rows hold distinct numbers below E (which experts a token id uses).  The
 reference has no such mode (its benchmarks run on uninitialised caches,
 v3/crates/rvllm-runtime/src/bring_up.rs:395-404); these are the distributions this
@@ -21,7 +21,7 @@ import torch
 from .safetensors_io import write_safetensors
 
 INIT_STD = {"matrix": (0.0, 0.02), "norm": (1.0, 0.1), "bias": (0.0, 0.02), "conv_taps": (0.0, 0.3), "coef": (0.5, 0.3),
-            "mixing": (0.0, 0.3)}
+            "mixing": (0.0, 0.3), "unit_scale": (0.7, 0.1)}
 
 
 def random_choice_table(shape, init: str, gen: torch.Generator) -> torch.Tensor:

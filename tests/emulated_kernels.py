@@ -52,7 +52,7 @@ class EmulatedKernels:
         return logits
 
     def latent_prepare(self, proj, c_gamma, eps, positions, cos, sin, slot_mapping, cache_layer, num_heads, head_dim, rot_dim,
-                       kv_rank, out_dtype, with_gate=True, write_kv=True):
+                       kv_rank, out_dtype, with_gate=True, write_kv=True, halves=False):
         T, row = proj.shape[0], kv_rank + rot_dim
         x = proj.float()
         qw = num_heads * (head_dim + rot_dim)
@@ -66,6 +66,11 @@ class EmulatedKernels:
             while c.dim() < v.dim():
                 c, s = c.unsqueeze(1), s.unsqueeze(1)
             out = v.clone()
+            if halves:    # pairs (i, i + half)
+                a, b = v[..., :half], v[..., half:2 * half]
+                out[..., :half] = a * c - b * s
+                out[..., half:2 * half] = b * c + a * s
+                return out
             a, b = v[..., 0:2 * half:2], v[..., 1:2 * half:2]
             out[..., 0:2 * half:2] = a * c - b * s
             out[..., 1:2 * half:2] = b * c + a * s
@@ -93,7 +98,7 @@ class EmulatedKernels:
         out.copy_(y.to(out.dtype))
         return out
 
-    def latent_attention(self, q_row, cache_layer, meta, num_heads, row, value_dim, scale, gate=None):
+    def latent_attention(self, q_row, cache_layer, meta, num_heads, row, value_dim, scale, gate=None, sinks=None):
         T = q_row.shape[0]
         ps = cache_layer.shape[3]
         out = torch.zeros((T, num_heads, value_dim), dtype=q_row.dtype)
@@ -109,22 +114,143 @@ class EmulatedKernels:
                 pages = [table[j // ps] for j in range(pos + 1)]
                 assert all(p >= 0 for p in pages), "attention reads a page that was given back"
                 rows = cache_layer[pages, 0, 0, [j % ps for j in range(pos + 1)], :].float()
-                p = torch.softmax((q_row[t].float() @ rows.T) * scale, -1)          # [heads, keys]
+                sc = (q_row[t].float() @ rows.T) * scale                            # [heads, keys]
+                if sinks is not None:
+                    p = torch.softmax(torch.cat([sc, sinks.float()[:, None]], dim=1), -1)[:, :-1]
+                else:
+                    p = torch.softmax(sc, -1)
                 o = p @ rows[:, :value_dim]
                 if gate is not None:
                     o = o * gate[t][:, None]
                 out[t] = o.to(q_row.dtype)
         return out
 
-    def moe_experts(self, x, chosen, gate_up, down, weight, add=None, out_dtype=None):
+    def moe_experts(self, x, chosen, gate_up, down, weight, add=None, out_dtype=None, weights=None, activation="silu"):
         T, ff = x.shape[0], gate_up.shape[1] // 2
         out = torch.zeros((T, x.shape[1])) if add is None else add.clone().float()
         for t in range(T):
-            for e in chosen[t].tolist():
+            for j, e in enumerate(chosen[t].tolist()):
                 gu = gate_up[e].float() @ x[t].float()
-                g, u = gu[:ff], gu[ff:]
-                out[t] += weight * (down[e].float() @ (g / (1.0 + torch.exp(-g)) * u).to(x.dtype).float())
+                if activation == "relu2":         # plain experts: every row of the first matrix is an up row
+                    a = torch.relu(gu) ** 2
+                else:
+                    g, u = gu[:ff], gu[ff:]
+                    a = g / (1.0 + torch.exp(-g)) * u
+                w = weight * (float(weights[t, j]) if weights is not None else 1.0)
+                out[t] += w * (down[e].float() @ a.to(x.dtype).float())
         return out.to(out_dtype or x.dtype)
+
+    # ---- the kernels of the Dynamic-Tanh norms, the unit-norm attention, the mLSTM and the routed experts
+    def dynamic_tanh(self, x, alpha, weight, bias, out_dtype=None):
+        return (torch.tanh(alpha * x.float()) * weight + bias).to(out_dtype or x.dtype)
+
+    def residual_dynamic_tanh(self, y, norm, x, next_norm, out_dtype):
+        x += self.dynamic_tanh(y.float(), *norm)
+        return x, (self.dynamic_tanh(x, *next_norm, out_dtype=out_dtype) if next_norm is not None else None)
+
+    def scale_rows(self, x, scale):
+        return x.float() * scale
+
+    def act_rows(self, u, activation, out_dtype, row_scale=None):
+        assert activation == "relu2"
+        a = torch.relu(u.float()) ** 2
+        if row_scale is not None:
+            a = a * row_scale[:, None]
+        return a.to(out_dtype)
+
+    def moe_route_top(self, scores, correction, experts, top, groups, keep, weight_eps, shared_gate=False):
+        s = torch.sigmoid(scores[:, :experts].float())
+        c = s + correction
+        per = experts // groups
+        gs = c.view(-1, groups, per).topk(min(2, per), dim=-1).values.sum(-1)
+        kept = gs.topk(keep, dim=-1).indices
+        allowed = torch.zeros_like(gs, dtype=torch.bool).scatter_(1, kept, True).repeat_interleave(per, dim=1)
+        chosen = c.masked_fill(~allowed, float("-inf")).topk(top, dim=-1).indices
+        w = s.gather(1, chosen)
+        w = w / (w.sum(-1, keepdim=True) + weight_eps)
+        gate = torch.sigmoid(scores[:, experts].float()) if shared_gate else None
+        return chosen.to(torch.int32), w, gate
+
+    def qk_unit_prepare(self, proj, eps, positions, cos, sin, slot_mapping, cache_layer, num_heads, num_kv_heads, head_dim,
+                        value_dim, slot_dim, out_dtype, halves=False, with_gate=True, write_kv=True):
+        T = proj.shape[0]
+        x = proj.float()
+        pos = positions.long()
+
+        def turn(v):           # [T, heads, head_dim]
+            if cos is None:
+                return v
+            half = cos.shape[1]
+            c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+            out = v.clone()
+            if halves:
+                a, b = v[..., :half], v[..., half:2 * half]
+                out[..., :half], out[..., half:2 * half] = a * c - b * s, b * c + a * s
+            else:
+                a, b = v[..., 0:2 * half:2], v[..., 1:2 * half:2]
+                out[..., 0:2 * half:2], out[..., 1:2 * half:2] = a * c - b * s, b * c + a * s
+            return out
+
+        unit = lambda v: v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+        qw = num_heads * head_dim
+        q = torch.zeros((T, num_heads, slot_dim))
+        q[:, :, :head_dim] = unit(turn(x[:, :qw].view(T, num_heads, head_dim)))
+        col = qw
+        if write_kv:
+            kw, vw = num_kv_heads * head_dim, num_kv_heads * value_dim
+            k = unit(turn(x[:, col:col + kw].view(T, num_kv_heads, head_dim)))
+            v = x[:, col + kw:col + kw + vw].view(T, num_kv_heads, value_dim)
+            col += kw + vw
+            ps = cache_layer.shape[3]
+            for t, slot in enumerate(slot_mapping.tolist()):
+                if slot < 0:
+                    continue
+                cache_layer[slot // ps, 0, :, slot % ps, :] = 0
+                cache_layer[slot // ps, 1, :, slot % ps, :] = 0
+                cache_layer[slot // ps, 0, :, slot % ps, :head_dim] = k[t].to(cache_layer.dtype)
+                cache_layer[slot // ps, 1, :, slot % ps, :value_dim] = v[t].to(cache_layer.dtype)
+        gate = torch.sigmoid(x[:, col:col + num_heads]) if with_gate else None
+        return q.view(T, num_heads * slot_dim).to(out_dtype), gate
+
+    def mlstm_scan(self, proj, i_col0, f_col0, i_bias, f_bias, cu_seqlens, state_slots, state, heads, head_dim, value_dim, cap):
+        T = proj.shape[0]
+        D, V = head_dim, value_dim
+        x = proj.float()
+        q = x[:, :heads * D].view(T, heads, D) * D ** -0.5
+        k = x[:, heads * D:2 * heads * D].view(T, heads, D)
+        v = torch.cat([x[:, 2 * heads * D:2 * heads * D + heads * V].view(T, heads, V), torch.ones((T, heads, 1))], dim=-1)
+        gi = cap * torch.tanh((x[:, i_col0:i_col0 + heads] + i_bias) / cap)
+        gf = torch.nn.functional.logsigmoid(cap * torch.tanh((x[:, f_col0:f_col0 + heads] + f_bias) / cap))
+        raw = torch.zeros((T, heads, V + 1))
+        top = torch.zeros((T, heads))
+        cu = cu_seqlens.tolist()
+        for s, slot in enumerate(state_slots.tolist()):
+            if slot < 0:
+                continue
+            S = state[slot, :heads * D * (V + 1)].view(heads, D, V + 1)
+            m = state[slot, heads * D * (V + 1):heads * D * (V + 1) + heads].clone()
+            for t in range(cu[s], cu[s + 1]):
+                new = torch.maximum(gf[t] + m, gi[t])
+                a, b = torch.exp(gf[t] + m - new), torch.exp(gi[t] - new)
+                S.copy_(a[:, None, None] * S + b[:, None, None] * k[t][:, :, None] * v[t][:, None, :])
+                m = new                      # (the state row keeps the old m until `mlstm_output` stores the last one)
+                raw[t] = torch.einsum("hdv,hd->hv", S, q[t])
+                top[t] = new
+        return raw.view(T, heads * (V + 1)), top
+
+    def mlstm_output(self, raw, top, gamma, eps, den_eps, proj, g_col0, heads, head_dim, value_dim, out_dtype, token_seq, cu_seqlens,
+                     state_slots, state):
+        T, V = raw.shape[0], value_dim
+        cu = cu_seqlens.tolist()
+        for s, slot in enumerate(state_slots.tolist()):
+            if slot >= 0 and cu[s + 1] > cu[s]:
+                at = heads * head_dim * (V + 1)
+                state[slot, at:at + heads] = top[cu[s + 1] - 1]
+        r = raw.view(T, heads, V + 1)
+        o = r[:, :, :V] / (torch.maximum(r[:, :, V:].abs(), torch.exp(-top)[:, :, None]) + den_eps)
+        o = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
+        z = proj[:, g_col0:g_col0 + heads * V].float()
+        return (o.reshape(T, heads * V) * gamma.float() * torch.sigmoid(z)).to(out_dtype)
 
     def act_mul(self, gate_up, activation, out_dtype=None, limit=None, alpha=None):
         inter = gate_up.shape[1] // 2
