@@ -9,7 +9,7 @@ a sliding window, a gate per head, and optionally another layer's keys and value
 
 What is cached is the key after rotation and norm, and the value.  A layer with `own_kv=False` has no key and value
 matrices: it reads the cache slot of the layer that the run order names, with its own queries, window, scale and gate; that
-slot keeps `kept_window` keys, the widest window among its readers.
+slot keeps `kept_window` keys, the widest window among its readers (None: all keys; default: this layer's window).
 
 A head's slot in the cache and in the attention kernels is `max(head_dim, value_dim)` wide; the shorter of key and value
 is followed by zeros (which change no score and add nothing to a result), and the output matrix gets zero columns where a
@@ -30,7 +30,7 @@ class UnitQkAttention(Part):
     PAIRS = ("neighbours", "halves")
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, scale: float,
-                 eps: float, window: Optional[int] = None, kept_window: Optional[int] = None, gate: bool = True,
+                 eps: float, window: Optional[int] = None, kept_window="window", gate: bool = True,
                  pairs: str = "neighbours", own_kv: bool = True, position=None, suffix: str = ""):
         from ..errors import ConfigError
         problems = []
@@ -40,14 +40,16 @@ class UnitQkAttention(Part):
             problems.append(f"key and value sizes are at most 256, got {head_dim} and {value_dim}")
         if pairs not in self.PAIRS:
             problems.append(f"rotation pairs {pairs!r} are not known ({', '.join(self.PAIRS)})")
-        if window is not None and kept_window is not None and kept_window < window:
-            problems.append(f"the cache keeps {kept_window} keys but the window spans {window}")
+        if kept_window == "window":                    # (None: the cache keeps every key, whatever this layer's window)
+            kept_window = window
+        if kept_window is not None and (window is None or kept_window < window):
+            problems.append(f"the cache keeps {kept_window} keys but the window spans {window or 'all of them'}")
         if problems:
             raise ConfigError(problems, "unit-norm attention")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
         self.head_dim, self.value_dim, self.slot_dim = head_dim, value_dim, max(head_dim, value_dim)
         self.scale, self.eps, self.window, self.has_gate, self.pairs, self.own_kv = scale, eps, window, gate, pairs, own_kv
-        self.kept_window = window if (kept_window is None and window is not None) else kept_window
+        self.kept_window = kept_window
         self.position = position
         outs, names = [num_heads * head_dim], ["q"]
         if own_kv:
