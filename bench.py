@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200: decode tokens per second, prefill, roofline.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--shape NAME]
-                    [--workload decode|serve|tufirax|vipelix|tibepel] [--impl ours|reference]
+                    [--workload decode|serve|tufirax|vipelix|tibepel|tugodra] [--impl ours|reference]
 
 The default run has the layer sizes of Llama-3.1-8B (32 layers, hidden 4096, 32 query heads,
 8 key/value heads of 128, MLP 14336, vocabulary 128256, llama3 rotary scaling) with random
@@ -789,6 +789,294 @@ def run_vipelix(args):
 
 
 # ---------------------------------------------------------------------------------------------------------
+# --workload tugodra: the Tugodra design (window attention with unit-norm queries and keys and borrowed keys, latent
+# attention with a sink, mLSTM matrix memories, Dynamic-Tanh norms around every sublayer, routed squared-relu experts with a
+# gated shared expert) at layer sizes that resemble real models, beside the Vipelix decoder of this engine - the closest
+# design: a float32 stream with a norm in front of and behind every sublayer, latent attention, experts plus a shared one -
+# at the same width, depth and experts; then each of the design's own kernels alone beside the like kernel of that path,
+# with its bytes or FLOPs over its time against the measured copy bandwidth or bf16 peak.  Random weights; its own JSON line.
+TUGODRA_SIZES = {
+    "2k": dict(width=2048, heads=16, kv=4, dim=128, window=1024, l_dim=128, rot=64, rank=192, m_heads=8, m_dim=128, m_vdim=256,
+               e_ff=1408, experts=16, top=2, groups=4, keep=2, shared=2816, layers=8),
+    "4k": dict(width=4096, heads=32, kv=8, dim=128, window=1024, l_dim=128, rot=64, rank=192, m_heads=16, m_dim=128, m_vdim=256,
+               e_ff=2048, experts=32, top=4, groups=8, keep=4, shared=4096, layers=8),
+}
+
+
+def tugodra_pair(size: dict, vocab: int = 32768):
+    """(Tugodra configuration, Vipelix configuration): layers of matrix memory, window attention, latent attention and a
+    window attention that borrows its keys, in turn, each with experts; beside as many Vipelix layers of experts."""
+    mlp = {"kind": "moe", "expert": {"ff": size["e_ff"]},
+           "router": {"experts": size["experts"], "top": size["top"], "groups": {"count": size["groups"], "keep": size["keep"]}},
+           "shared": {"ff": size["shared"]}}
+    att = {"heads": size["heads"], "kv_heads": size["kv"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** 0.5 * 0.1,
+           "mask": {"size": size["window"]}, "rot": {"dims": size["dim"], "base": 1e6}}
+    lat = {"heads": size["heads"], "dim": size["l_dim"], "rot_dim": size["rot"], "vdim": size["l_dim"], "kv_rank": size["rank"],
+           "scale": (size["l_dim"] + size["rot"]) ** -0.5, "rot": {"dims": size["rot"], "base": 500000.0}}
+    mem = {"heads": size["m_heads"], "dim": size["m_dim"], "vdim": size["m_vdim"], "gate_cap": 15.0}
+    layers = []
+    for i in range(size["layers"]):
+        k = i % 4
+        if k == 0:
+            layers.append({"type": "mlstm", "mixer": mem, "mlp": mlp})
+        elif k == 1:
+            layers.append({"type": "attention", "mixer": att, "mlp": mlp})
+        elif k == 2:
+            layers.append({"type": "latent_attention", "mixer": lat, "mlp": mlp})
+        else:
+            layers.append({"type": "attention", "mixer": dict(att, kv_from=i - 2), "mlp": mlp})
+    tug = {"architecture": "Tugodra", "width": size["width"], "vocab": vocab, "norm": {"eps": 1e-6}, "embedding": {"scale": size["width"] ** 0.5},
+           "layers": layers}
+    vmoe = {"type": "latent_attention", "mixer": dict(lat),
+            "mlp": {"kind": "moe", "expert": {"ff": size["e_ff"]}, "router": {"experts": size["experts"], "top": size["top"]},
+                    "shared": {"ff": size["shared"]}}}
+    vip = {"architecture": "Vipelix", "width": size["width"], "vocab": vocab, "norm": {"eps": 1e-6}, "layers": [vmoe] * size["layers"]}
+    return tug, vip
+
+
+def run_tugodra(args):
+    import torch
+
+    from rvllm_b200 import LLM, config_from_dict
+    from rvllm_b200.engine import StepEntry
+    from rvllm_b200.kernels import AttentionMeta
+
+    peaks = measured_peaks()
+    PROMPT, CTX, batch = 2048, 4096, args.batch
+    gen = torch.Generator().manual_seed(0)
+    out = {"workload": "tugodra", "dtype": "bf16", "data": "synthetic", "peaks": peaks["source"], "prompt_len": PROMPT, "batch": batch,
+           "steps": args.steps, "warmup": args.warmup, "models": {}, "kernels": {}}
+
+    def measure(cfg_dict):
+        config = config_from_dict(cfg_dict)
+        llm = LLM(config=config, random_weights=True, seed=0, dtype="bfloat16", block_size=16, num_blocks=batch * (CTX // 16) + 8,
+                  max_model_len=CTX, max_num_seqs=batch, max_num_batched_tokens=PROMPT, enforce_eager=args.eager)
+        runner, V = llm.engine.runner, llm.engine.spec.vocab_size
+        p = torch.randint(0, V, (PROMPT,), generator=gen).tolist()
+        for _ in range(3):
+            runner.step([StepEntry("w", p, [PROMPT - 1])])
+            runner.finish("w")
+        torch.cuda.synchronize()
+        pf = []
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step([StepEntry("p", p, [PROMPT - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.finish("p")
+            pf.append(a.elapsed_time(b))
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, torch.randint(0, V, (PROMPT,), generator=gen).tolist(), [])])
+        for _ in range(args.warmup):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            runner.step([StepEntry(r, [1], [0]) for r in ids])
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        for rid in ids:
+            runner.finish(rid)
+        kernels = llm.engine.kernels
+        kernels.raise_on_abort()
+        del llm
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(min(pf), 3), "prefill_tok_s": round(PROMPT / (min(pf) / 1e3), 1),
+                "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms / 1e3), 1)}, kernels
+
+    K = None
+    for name in (args.sizes.split(",") if args.sizes else list(TUGODRA_SIZES)):
+        tug, vip = tugodra_pair(TUGODRA_SIZES[name])
+        a, K = measure(tug)
+        b, K = measure(vip)
+        out["models"][name] = {"tugodra": a, "vipelix_same_size": b, "layers": TUGODRA_SIZES[name]["layers"],
+                               "prefill_ratio": round(a["prefill_tok_s"] / b["prefill_tok_s"], 3),
+                               "decode_ratio": round(a["decode_tok_s"] / b["decode_tok_s"], 3)}
+    if K is None:
+        from rvllm_b200.kernels import get_library
+        K = get_library("cuda:0")
+
+    # ---- the design's kernels alone, at the "4k" sizes, beside the like kernel of the Vipelix path ----------------
+    torch.manual_seed(0)
+    z = TUGODRA_SIZES["4k"]
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bw, peak = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+
+    def by_bytes(name, ms, nbytes, like=None):
+        out["kernels"][name] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1), "frac_hbm": round(nbytes / (ms / 1e3) / bw, 3)}
+        if like is not None:
+            out["kernels"][name]["like"] = like
+
+    def by_flops(name, ms, flops, like=None):
+        out["kernels"][name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_bf16": round(flops / (ms / 1e3) / peak, 3)}
+        if like is not None:
+            out["kernels"][name]["like"] = like
+
+    def like_bytes(kernel, ms, nbytes):
+        return {"kernel": kernel, "ms": round(ms, 4), "frac_hbm": round(nbytes / (ms / 1e3) / bw, 3)}
+
+    def like_flops(kernel, ms, flops):
+        return {"kernel": kernel, "ms": round(ms, 4), "frac_bf16": round(flops / (ms / 1e3) / peak, 3)}
+
+    T, W = PROMPT, z["width"]
+    H, G, D, WIN = z["heads"], z["kv"], z["dim"], z["window"]
+    # -- the sum with both norms
+    y, res = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+    g = torch.ones(W, dtype=bf, device=dev)
+    dyt = (torch.full((1,), 0.7, device=dev), torch.ones(W, device=dev), torch.zeros(W, device=dev))
+    ms_like = _time_kernel(lambda: K.residual_rmsnorm(y, g, 1e-6, res, bf, next_norm=(g, 1e-6)), flush=flush)
+    by_bytes("residual_dynamic_tanh_then_norm", _time_kernel(lambda: K.residual_dynamic_tanh(y, dyt, res, dyt, bf), flush=flush),
+             T * W * (4 + 4 + 4 + 2), like_bytes("residual_rmsnorm with the next norm", ms_like, T * W * (4 + 4 + 4 + 2)))
+    xf = torch.randn(T, W, device=dev)
+    xb = xf.to(bf)
+    ms_like = _time_kernel(lambda: K.rmsnorm(xf, g, 1e-6, out_dtype=bf), flush=flush)
+    by_bytes("dynamic_tanh", _time_kernel(lambda: K.dynamic_tanh(xf, *dyt, out_dtype=bf), flush=flush), T * W * 6,
+             like_bytes("rmsnorm", ms_like, T * W * 6))
+
+    # -- rotation, unit norm and cache write of the window attention beside the latent's prepare kernel
+    pages = PROMPT // 16
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+
+    def tables(dims, base):
+        ang = torch.arange(T, dtype=torch.float64)[:, None] * torch.tensor([base ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=torch.float64)[None, :]
+        return torch.cos(ang).float().to(dev), torch.sin(ang).float().to(dev)
+
+    cos, sin = tables(D, 1e6)
+    proj = torch.randn(T, H * D + 2 * G * D + H, device=dev)
+    cache2 = torch.zeros(pages, 2, G, 16, D, dtype=bf, device=dev)
+    LD, RD, R = z["l_dim"], z["rot"], z["rank"]
+    ROW = R + RD
+    cos_l, sin_l = tables(RD, 500000.0)
+    proj_l = torch.randn(T, H * (LD + RD) + ROW, device=dev)
+    cache1 = torch.zeros(pages, 1, 1, 16, ROW, dtype=bf, device=dev)
+    gamma = torch.ones(R, dtype=bf, device=dev)
+    ms_like = _time_kernel(lambda: K.latent_prepare(proj_l, gamma, 1e-6, pos, cos_l, sin_l, pos, cache1, H, LD, RD, R, bf, with_gate=False, halves=True), flush=flush)
+    by_bytes("qk_unit_prepare", _time_kernel(lambda: K.qk_unit_prepare(proj, 1e-6, pos, cos, sin, pos, cache2, H, G, D, D, D, bf), flush=flush),
+             T * (proj.shape[1] * 4 + (H + 2 * G) * D * 2 + H * 4),
+             like_bytes("latent_prepare", ms_like, T * (proj_l.shape[1] * 4 + (H * (LD + RD) + ROW) * 2)))
+
+    # -- attention inside a window (the engine's attention kernels with a window and a gate) beside the same kernels without
+    def paged_case(q_len, ctx, seqs):
+        n = seqs * (ctx // 16)
+        cache = torch.randn(n, 2, G, 16, D, device=dev).to(bf)
+        tbl = torch.arange(n, dtype=torch.int32, device=dev).view(seqs, ctx // 16)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        meta = AttentionMeta(tbl, cu, torch.full((seqs,), ctx, dtype=torch.int32, device=dev),
+                             torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len), None, seqs, q_len, ctx, 16,
+                             seqs if q_len == 1 else 0)
+        return torch.randn(seqs * q_len, H * D, device=dev).to(bf), cache, meta, torch.rand(seqs * q_len, H, device=dev)
+
+    q, cache, meta, gate = paged_case(PROMPT, PROMPT, 1)
+    ms_like = _time_kernel(lambda: K.paged_attention(q, cache, meta, H, G, D, 0.09, None), flush=flush)
+    seen = sum(min(i + 1, WIN) for i in range(PROMPT))
+    by_flops("window_attention_prefill", _time_kernel(lambda: K.paged_attention(q, cache, meta, H, G, D, 1.1, WIN, gate=gate), flush=flush),
+             4.0 * H * D * seen, like_flops("attention_prefill without a window", ms_like, 4.0 * H * D * PROMPT * PROMPT / 2))
+    q, cache, meta, gate = paged_case(1, PROMPT, batch)
+    ms_like = _time_kernel(lambda: K.paged_attention(q, cache, meta, H, G, D, 0.09, None), flush=flush)
+    by_bytes("window_attention_decode", _time_kernel(lambda: K.paged_attention(q, cache, meta, H, G, D, 1.1, WIN, gate=gate), flush=flush),
+             batch * WIN * 2 * G * D * 2, like_bytes("attention_decode without a window", ms_like, batch * PROMPT * 2 * G * D * 2))
+
+    # -- latent attention with a sink beside the same kernel with a gate
+    def latent_case(q_len, ctx, seqs):
+        n = seqs * (ctx // 16)
+        cache = torch.randn(n, 1, 1, 16, ROW, device=dev).to(bf)
+        tbl = torch.arange(n, dtype=torch.int32, device=dev).view(seqs, ctx // 16)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        meta = AttentionMeta(tbl, cu, torch.full((seqs,), ctx, dtype=torch.int32, device=dev),
+                             torch.arange(seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len), None, seqs, q_len, ctx, 16,
+                             seqs if q_len == 1 else 0)
+        return torch.randn(seqs * q_len, H, ROW, device=dev).to(bf), cache, meta, torch.rand(seqs * q_len, H, device=dev)
+
+    sink = torch.zeros(H, device=dev)
+    q, cache, meta, gate = latent_case(PROMPT, PROMPT, 1)
+    ms_like = _time_kernel(lambda: K.latent_attention(q, cache, meta, H, ROW, R, 0.07, gate=gate), flush=flush)
+    fl = 2.0 * H * (ROW + R) * PROMPT * PROMPT / 2
+    by_flops("latent_attention_sink_prefill", _time_kernel(lambda: K.latent_attention(q, cache, meta, H, ROW, R, 0.07, sinks=sink), flush=flush), fl,
+             like_flops("latent_attention with a gate", ms_like, fl))
+    q, cache, meta, gate = latent_case(1, PROMPT, batch)
+    ms_like = _time_kernel(lambda: K.latent_attention(q, cache, meta, H, ROW, R, 0.07, gate=gate), flush=flush)
+    by_bytes("latent_attention_sink_decode", _time_kernel(lambda: K.latent_attention(q, cache, meta, H, ROW, R, 0.07, sinks=sink), flush=flush),
+             batch * PROMPT * ROW * 2, like_bytes("latent_attention with a gate", ms_like, batch * PROMPT * ROW * 2))
+
+    # -- the matrix memory beside the gated delta rule (the engine's other matrix-valued recurrence) at equal sizes
+    MH, MD, MV = z["m_heads"], z["m_dim"], z["m_vdim"]
+    cols = 2 * MH * MD + 2 * MH * MV + 2 * MH
+    ib, fb, mnorm = torch.zeros(MH, device=dev), torch.full((MH,), 3.0, device=dev), torch.ones(MH * MV, device=dev)
+
+    def memory_case(q_len, seqs):
+        pr = torch.randn(seqs * q_len, cols, device=dev)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        seq = slots.repeat_interleave(q_len)
+        st = torch.zeros(seqs, MH * MD * (MV + 1) + MH, device=dev)
+        return pr, cu, slots, seq, st
+
+    def delta_case(q_len, seqs):
+        qkv = torch.randn(seqs * q_len, 2 * MH * MD + MH * MV, device=dev).to(bf)
+        pr = torch.randn(seqs * q_len, 2 * MH, device=dev)
+        cu = torch.arange(seqs + 1, dtype=torch.int32, device=dev) * q_len
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        st = torch.zeros(seqs, MH * MD * MV, device=dev)
+        return qkv, pr, cu, slots, st
+
+    alog, dtb = torch.zeros(MH, device=dev), torch.zeros(MH, device=dev)
+    gcol = 2 * MH * MD + MH * MV
+    for label, q_len, seqs in (("prefill", PROMPT, 1), ("decode", 1, batch)):
+        pr, cu, slots, seq, st = memory_case(q_len, seqs)
+        qkv, pr2, cu2, slots2, st2 = delta_case(q_len, seqs)
+        state_bytes = seqs * MH * MD * (MV + 1) * 4 * 2
+        io_bytes = seqs * q_len * (2 * MH * MD + MH * MV + MH * (MV + 1)) * 4
+        ms_like = _time_kernel(lambda: K.delta_rule(qkv, pr2, 0, MH, alog, dtb, cu2, slots2, st2, MH, MH, MD, MV, 1e-6), flush=flush)
+        lk = like_bytes("delta_rule", ms_like, seqs * MH * MD * MV * 8 + seqs * q_len * ((2 * MH * MD + MH * MV) * 2 + MH * MV * 4))
+        by_bytes(f"mlstm_scan_{label}", _time_kernel(lambda: K.mlstm_scan(pr, gcol + MH * MV, gcol + MH * MV + MH, ib, fb, cu, slots, st, MH, MD, MV, 15.0), flush=flush),
+                 state_bytes + io_bytes, lk)
+        raw, top = K.mlstm_scan(pr, gcol + MH * MV, gcol + MH * MV + MH, ib, fb, cu, slots, st, MH, MD, MV, 15.0)
+        o = torch.randn(seqs * q_len, MH * MV, device=dev)
+        gam = torch.ones(MV, dtype=bf, device=dev)
+        prg = torch.randn(seqs * q_len, MH * MV, device=dev)
+        ms_like = _time_kernel(lambda: K.head_norm_gate(o, gam, 1e-6, prg, 0, MH, MV, bf), flush=flush)
+        n_el = seqs * q_len * MH * MV
+        by_bytes(f"mlstm_output_{label}", _time_kernel(lambda: K.mlstm_output(raw, top, mnorm, 1e-6, 1e-6, pr, gcol, MH, MD, MV, bf, seq, cu, slots, st), flush=flush),
+                 n_el * (4 + 4 + 2), like_bytes("head_norm_gate", ms_like, n_el * (4 + 4 + 2)))
+
+    # -- the router, and the experts beside the gated experts of the like design
+    E, top_k, EF = z["experts"], z["top"], z["e_ff"]
+    logits = torch.randn(T, E + 1, device=dev)
+    corr = torch.zeros(E, device=dev)
+    table = torch.rand(32768, E, device=dev).argsort(1)[:, :top_k].to(torch.int32).contiguous()
+    tokens = torch.randint(0, 32768, (T,), device=dev, dtype=torch.int32)
+    ms_like = _time_kernel(lambda: K.gather_rows(table, tokens), flush=flush)
+    by_bytes("moe_route_top", _time_kernel(lambda: K.moe_route_top(logits, corr, E, top_k, z["groups"], z["keep"], 1e-20, shared_gate=True), flush=flush),
+             T * ((E + 1) * 4 + top_k * 8 + 4), like_bytes("gather_rows of a choice table", ms_like, T * top_k * 8))
+    chosen, wts, _ = K.moe_route_top(logits, corr, E, top_k, z["groups"], z["keep"], 1e-20, shared_gate=True)
+    up, down = torch.randn(E, EF, W, device=dev).to(bf) * 0.02, torch.randn(E, W, EF, device=dev).to(bf) * 0.02
+    gate_up = torch.randn(E, 2 * EF, W, device=dev).to(bf) * 0.02
+    ms_like = _time_kernel(lambda: K.moe_experts(xb, chosen, gate_up, down, 1.0 / top_k, out_dtype=torch.float32), flush=flush)
+    by_flops("routed_experts_prefill", _time_kernel(lambda: K.moe_experts(xb, chosen, up, down, 1.0, out_dtype=torch.float32, weights=wts, activation="relu2"), flush=flush),
+             4.0 * T * top_k * EF * W, like_flops("gated experts chosen by table", ms_like, 6.0 * T * top_k * EF * W))
+    xd, cd, wd = xb[:batch].contiguous(), chosen[:batch].contiguous(), wts[:batch].contiguous()
+    touched = len(set(cd.flatten().tolist()))
+    ms_like = _time_kernel(lambda: K.moe_experts(xd, cd, gate_up, down, 1.0 / top_k, out_dtype=torch.float32), flush=flush)
+    by_bytes("routed_experts_decode", _time_kernel(lambda: K.moe_experts(xd, cd, up, down, 1.0, out_dtype=torch.float32, weights=wd, activation="relu2"), flush=flush),
+             touched * 2 * EF * W * 2, like_bytes("gated experts chosen by table", ms_like, touched * 3 * EF * W * 2))
+    out["kernels"]["routed_experts_decode"]["experts_touched"] = touched
+    SF = z["shared"]
+    u = torch.randn(T, SF, device=dev)
+    gub = torch.randn(T, 2 * SF, device=dev).to(bf)
+    sg = torch.rand(T, device=dev)
+    ms_like = _time_kernel(lambda: K.silu_mul(gub), flush=flush)
+    by_bytes("act_rows", _time_kernel(lambda: K.act_rows(u, "relu2", bf, row_scale=sg), flush=flush), T * SF * 6,
+             like_bytes("silu_mul", ms_like, T * SF * 6))
+    K.raise_on_abort()
+    print(json.dumps(out))
+
+
+# ---------------------------------------------------------------------------------------------------------
 # --workload tibepel: the Tibepel design (chunked attention whose softmax weights are mixed across the heads beside a
 # gated delta rule, mamba1 scans, clamped gated feed-forwards, a per-token side input, a float32 stream) at layer sizes that
 # resemble real models, beside the Tufirax design of this engine - the closest one: attention and state-space layers
@@ -1010,10 +1298,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (both numbers are reported)")
     ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes of the model")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax", "vipelix", "tibepel"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "tufirax", "vipelix", "tibepel", "tugodra"],
                     help="decode: the benchmark's one JSON line; serve: continuous batching of uneven prompts; tufirax, vipelix, tibepel: "
                          "that design at real layer sizes beside the closest decoder of equal size, and its kernels alone")
-    ap.add_argument("--sizes", default="", help="tufirax, vipelix, tibepel: which sizes to run, with commas (default: all)")
+    ap.add_argument("--sizes", default="", help="tufirax, vipelix, tibepel, tugodra: which sizes to run, with commas (default: all)")
     ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")
     ap.add_argument("--output-len", type=int, default=256, help="serve: tokens generated per request")
     ap.add_argument("--budget", type=int, default=2048, help="serve: tokens per step")
@@ -1037,6 +1325,8 @@ def main():
         run_vipelix(args)
     elif args.workload == "tibepel":
         run_tibepel(args)
+    elif args.workload == "tugodra":
+        run_tugodra(args)
     elif args.workload == "serve":
         run_serve(args)
     else:

@@ -98,6 +98,9 @@ class ModelSpec:
     # blocks then round a copy for their products); None: the stream has the activations' type
     eos_token_ids: Tuple[int, ...] = ()
     residual_dtype: Optional[str] = None
+    # False: the kernels of this model's steps are launched one strictly after the other, without programmatic dependent
+    # launch (a kernel's set-up then does not overlap the tail of the kernel before it)
+    programmatic_launch: bool = True
 
     def validate(self) -> List[str]:
         problems = []

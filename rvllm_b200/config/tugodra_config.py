@@ -271,4 +271,8 @@ class TugodraConfig:
             position_encodings={key: PartSpec("rotary", {"head_dim": dims, "theta": base, "rotary_dim": dims})
                                 for (dims, base), key in rotations.items()},
             embedding_hooks=(PartSpec("embedding_scale", {"scale": self.embedding_scale}),),
-            residual_dtype="float32", eos_token_ids=self.eos_token_ids)
+            residual_dtype="float32", eos_token_ids=self.eos_token_ids,
+            # steps of this design at real layer widths stopped answering, rarely, with programmatic dependent launch on
+            # and never with it off; one cause was found and removed (a kernel that signalled its dependents before it
+            # held its tensor memory), another may remain: its kernels follow one another strictly
+            programmatic_launch=False)

@@ -188,7 +188,6 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint32_t& tmem_base_slot = *reinterpret_cast<uint32_t*>(bars + 30);
     volatile int& abort_flag = *reinterpret_cast<volatile int*>(bars + 31);
 
-    rv_pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) { tma_prefetch_descriptor(&map_q); tma_prefetch_descriptor(&map_kv); }
     const uint32_t bar_q = smem_u32(&bars[B_Q]), bar_k0 = smem_u32(&bars[B_K]);
@@ -252,6 +251,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    // The kernels behind this one may start only now that this CTA holds its tensor memory (a CTA that leaves early
+    // counts as having signalled).  This kernel allocates after its wait; a kernel launched behind it allocates before its
+    // own wait and then waits for this grid: signalled at the top, such a CTA could take the columns that a CTA of this
+    // grid on the same SM still has to ask for, and neither would ever finish.
+    rv_pdl_launch_dependents();
 
     const int box_keys = p.page_size < KV_TILE ? p.page_size : KV_TILE;     // keys one TMA box brings
     const int boxes = KV_TILE / box_keys;

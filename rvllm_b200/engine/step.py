@@ -305,6 +305,12 @@ class ModelRunner:
             max_ctx_len=ctx_limit or self.max_model_len, page_size=ps, num_decode=B) for (o_slot, o_bt) in group_offsets]
         return ctx
 
+    def _apply_launch_mode(self) -> None:
+        """Tell the kernel library, which the engines of a process share, how this model's kernels follow one another."""
+        set_pdl = getattr(self.kernels, "set_pdl", None)
+        if set_pdl is not None:
+            set_pdl(getattr(getattr(self.model, "spec", None), "programmatic_launch", True))
+
     def step(self, entries: Sequence[StepEntry], late_tokens=None) -> Optional[torch.Tensor]:
         """Run the batch.  Returns float32 logits [wanted places, vocab] in the order of the
         entries and of each entry's `want` (None if nothing is wanted).
@@ -315,6 +321,7 @@ class ModelRunner:
         if not entries:
             return None
         self.validate(entries)
+        self._apply_launch_mode()
         if late_tokens is not None:
             if len(late_tokens[1]) != len(entries):
                 raise SchedulerError(f"{len(entries)} entries but {len(late_tokens[1])} late-token indices")
@@ -408,6 +415,7 @@ class ModelRunner:
         write nothing, so live requests are not disturbed.  Returns the number of graphs captured."""
         if not self.graph_batch_sizes or self.device.type != "cuda" or not getattr(self.model, "graph_safe", True):
             return 0
+        self._apply_launch_mode()
         limit = min(max_context or self.max_model_len, self.max_model_len)
         ctx_buckets, b = [], self._ctx_bucket(1)
         while True:

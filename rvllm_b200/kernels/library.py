@@ -105,6 +105,7 @@ class CudaKernels:
     FUSED_NORM_MAX_ROWS = 0 # rows up to which an RMSNorm is applied inside the decode GEMM that consumes it
     FUSED_QKV_MAX_ROWS = 64 # rows up to which q/k/v product, rotation and cache write are one kernel
     pdl = os.environ.get("RVLLM_NO_PDL") != "1"   # programmatic dependent launch between kernels
+    no_pdl_for = tuple(n for n in os.environ.get("RVLLM_NO_PDL_FOR", "").split(",") if n)   # ... but not for these source files
     num_sms = 148           # SMs of the device; asked from the device when the library is made
 
     def __init__(self, device="cuda:0"):
@@ -119,6 +120,7 @@ class CudaKernels:
         torch.backends.cudnn.allow_tf32 = False
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self._libs = {}
+        self._pdl_allowed = True     # a model may switch programmatic dependent launch off for its steps (`set_pdl`)
         self._decode_counters = None
         # one status word for every tcgen05 launch of the engine: a kernel whose bounded wait on an
         # mbarrier gave up writes a non-zero code here instead of hanging (see `raise_on_abort`)
@@ -130,12 +132,25 @@ class CudaKernels:
         lib = self._libs.get(key)
         if lib is None:
             lib = build.load_library(source, defines)
-            lib.rv_set_pdl(c_int(1 if self.pdl else 0))
+            lib.rv_set_pdl(c_int(1 if (self.pdl and self._pdl_allowed and source not in self.no_pdl_for) else 0))
             if source == "gemm_tcgen05_decode.cu":
-                lib.rv_gemm_decode_set_l2_ahead(c_int(self.DECODE_L2_AHEAD if self.pdl else 0))
+                lib.rv_gemm_decode_set_l2_ahead(c_int(self.DECODE_L2_AHEAD if (self.pdl and self._pdl_allowed) else 0))
                 lib.rv_gemm_decode_set_k_rotate(c_int(self.DECODE_K_ROTATE))
             self._libs[key] = lib
         return lib
+
+    def set_pdl(self, allowed: bool) -> None:
+        """Allow or forbid programmatic dependent launch for every kernel launched from now on (the class switch `pdl`
+        and the per-source exceptions still apply).  An engine calls this for its model before it runs a step."""
+        allowed = bool(allowed)
+        if allowed == self._pdl_allowed:
+            return
+        self._pdl_allowed = allowed
+        for (source, _), lib in self._libs.items():
+            on = self.pdl and allowed and source not in self.no_pdl_for
+            lib.rv_set_pdl(c_int(1 if on else 0))
+            if source == "gemm_tcgen05_decode.cu":
+                lib.rv_gemm_decode_set_l2_ahead(c_int(self.DECODE_L2_AHEAD if on else 0))
 
     @staticmethod
     def _stream():
