@@ -8,8 +8,9 @@
 // of S one by one, so a column is the work of `parts` lanes with NS entries each (registers), whose partial sums meet by
 // shuffles.  Grid (column blocks, heads, sequences), 128 threads.  q, k of ML_CHUNK tokens and the tokens' a and b wait in
 // shared memory; a lane's NS entries of a row start at a multiple of NS + 4 floats, so that the 16-byte reads of the
-// lanes of a column fall on different banks.  The gates of a chunk are formed side by side, then one thread walks the
-// maximum through the chunk.  State row of a request: [heads][d][vd + 1], then m [heads]; all float32.
+// lanes of a column fall on different banks.  The gates of a chunk are formed side by side, one thread walks the maximum
+// through the chunk (an add and a max a token), and the exponentials are again formed side by side; the next chunk's raw
+// inputs wait in registers behind the walk.  State row of a request: [heads][d][vd + 1], then m [heads]; all float32.
 //
 //   mlstm_scan     raw [tokens, heads x (vd + 1)] and top [tokens, heads] (m_t) from the float32 projection
 //   mlstm_output   o = raw / (max(|n . q|, exp(-m)) + den_eps);  o / sqrt(mean(o^2) + eps) per head, times a weight per
@@ -18,8 +19,13 @@
 #include "common.cuh"
 
 #define ML_CHUNK 16
+#define ML_PRE_Q 4          // q (and k) elements per lane and token that the prefetch holds: d <= 32 * ML_PRE_Q
+#define ML_PRE_V 8          // values per thread and chunk that the prefetch holds: 128 / parts <= 8 * ML_PRE_V
 
-template <int NS>
+// PRE: the raw inputs of the next chunk are loaded into registers before the current chunk is walked, so that their way
+// from memory lies behind the walk; without it (wider keys, or more columns per block than the registers hold) a chunk
+// is loaded when its turn comes.
+template <int NS, bool PRE>
 __global__ void __launch_bounds__(128)
 mlstm_scan_kernel(const float* __restrict__ proj, int stride, int i_col0, int f_col0, const float* __restrict__ i_bias,
                   const float* __restrict__ f_bias, const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
@@ -39,7 +45,8 @@ mlstm_scan_kernel(const float* __restrict__ proj, int stride, int i_col0, int f_
     float* sB = sA + ML_CHUNK;                             // [ML_CHUNK] weight of the new outer product
     float* sI = sB + ML_CHUNK;                             // [ML_CHUNK] log input gate
     float* sF = sI + ML_CHUNK;                             // [ML_CHUNK] log forget gate
-    float* sV = sF + ML_CHUNK;                             // [ML_CHUNK][128 / parts]: the chunk's values of the block's columns
+    float* sM = sF + ML_CHUNK;                             // [ML_CHUNK + 1] the running maximum before and after each token
+    float* sV = sM + ML_CHUNK + 4;                         // [ML_CHUNK][128 / parts]: the chunk's values of the block's columns
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int per_block = 128 / parts;
     // a warp holds 32 / parts neighbouring columns; the `parts` lanes of a column lie 32 / parts lanes apart, so that
@@ -62,37 +69,101 @@ mlstm_scan_kernel(const float* __restrict__ proj, int stride, int i_col0, int f_
     float m = *mrow;                                       // (every thread reads it; thread 0 carries it)
     const float bi = i_bias[h], bf = f_bias[h];
     const float inv_cap = 1.0f / cap;
+    float pq[ML_CHUNK / 4][ML_PRE_Q], pk[ML_CHUNK / 4][ML_PRE_Q], pv[ML_PRE_V];
+    float pgi = 0.f, pgf = 0.f;
+    auto load_chunk = [&](int t0) {                       // PRE only: the chunk's raw q, k (a warp per token), v and gate logits
+        const int nt = min(ML_CHUNK, n_tok - t0);
+#pragma unroll
+        for (int x = 0; x < ML_CHUNK / 4; ++x) {
+            const int tt = warp + 4 * x;
+            const size_t row = (size_t)(start + t0 + tt) * stride + (size_t)h * d;
+#pragma unroll
+            for (int y = 0; y < ML_PRE_Q; ++y) {
+                const int e = lane + 32 * y;
+                pq[x][y] = 0.f; pk[x][y] = 0.f;
+                if (tt < nt && e < d) {
+                    pq[x][y] = proj[row + e];
+                    pk[x][y] = proj[row + qk + e];
+                }
+            }
+        }
+#pragma unroll
+        for (int y = 0; y < ML_PRE_V; ++y) {
+            const int i = tid + 128 * y;
+            const int tt = i / per_block, cc = blockIdx.x * per_block + (i - tt * per_block);
+            pv[y] = 0.f;
+            if (tt < nt && cc <= vd) pv[y] = cc < vd ? proj[(size_t)(start + t0 + tt) * stride + 2 * qk + (size_t)h * vd + cc] : 1.f;
+        }
+        if (tid < nt) {
+            const size_t row = (size_t)(start + t0 + tid) * stride;
+            pgi = proj[row + i_col0 + h];
+            pgf = proj[row + f_col0 + h];
+        }
+    };
+    auto gates = [&](float raw_i, float raw_f, int at) {
+        const float gi = cap * tanhf((raw_i + bi) * inv_cap);
+        const float x = cap * tanhf((raw_f + bf) * inv_cap);
+        sI[at] = gi;
+        sF[at] = x < 0.f ? x - log1pf(expf(x)) : -log1pf(expf(-x));          // log sigmoid
+    };
+    const bool pre = PRE && n_tok > ML_CHUNK;            // (a short portion, a decode step's single token: loaded when its turn comes)
+    if (pre) load_chunk(0);
     for (int t0 = 0; t0 < n_tok; t0 += ML_CHUNK) {
         const int nt = min(ML_CHUNK, n_tok - t0);
         __syncthreads();
-        if (tid < nt) {
-            const size_t row = (size_t)(start + t0 + tid) * stride;
-            const float gi = cap * tanhf((proj[row + i_col0 + h] + bi) * inv_cap);
-            const float x = cap * tanhf((proj[row + f_col0 + h] + bf) * inv_cap);
-            sI[tid] = gi;
-            sF[tid] = x < 0.f ? x - log1pf(expf(x)) : -log1pf(expf(-x));          // log sigmoid
-        }
-        for (int tt = warp; tt < nt; tt += 4) {                                   // a warp per token: q and k of the head
-            const size_t row = (size_t)(start + t0 + tt) * stride + (size_t)h * d;
-            for (int e = lane; e < d; e += 32) {
-                const int at = tt * row_floats + (e / NS) * (NS + 4) + (e % NS);
-                sQ[at] = proj[row + e] * q_scale;
-                sK[at] = proj[row + qk + e];
+        if (pre) {
+#pragma unroll
+            for (int x = 0; x < ML_CHUNK / 4; ++x) {
+                const int tt = warp + 4 * x;
+#pragma unroll
+                for (int y = 0; y < ML_PRE_Q; ++y) {
+                    const int e = lane + 32 * y;
+                    if (tt < nt && e < d) {
+                        const int at = tt * row_floats + (e / NS) * (NS + 4) + (e % NS);
+                        sQ[at] = pq[x][y] * q_scale;
+                        sK[at] = pk[x][y];
+                    }
+                }
             }
-        }
-        for (int i = tid; i < nt * per_block; i += 128) {
-            const int tt = i / per_block, cc = blockIdx.x * per_block + (i - tt * per_block);
-            sV[i] = cc < vd ? proj[(size_t)(start + t0 + tt) * stride + 2 * qk + (size_t)h * vd + cc] : (cc == vd ? 1.f : 0.f);
+#pragma unroll
+            for (int y = 0; y < ML_PRE_V; ++y) {
+                const int i = tid + 128 * y;
+                if (i < ML_CHUNK * per_block) sV[i] = pv[y];
+            }
+            if (tid < nt) gates(pgi, pgf, tid);
+        } else {
+            if (tid < nt) {
+                const size_t row = (size_t)(start + t0 + tid) * stride;
+                gates(proj[row + i_col0 + h], proj[row + f_col0 + h], tid);
+            }
+            for (int tt = warp; tt < nt; tt += 4) {                                   // a warp per token: q and k of the head
+                const size_t row = (size_t)(start + t0 + tt) * stride + (size_t)h * d;
+                for (int e = lane; e < d; e += 32) {
+                    const int at = tt * row_floats + (e / NS) * (NS + 4) + (e % NS);
+                    sQ[at] = proj[row + e] * q_scale;
+                    sK[at] = proj[row + qk + e];
+                }
+            }
+            for (int i = tid; i < nt * per_block; i += 128) {
+                const int tt = i / per_block, cc = blockIdx.x * per_block + (i - tt * per_block);
+                sV[i] = cc < vd ? proj[(size_t)(start + t0 + tt) * stride + 2 * qk + (size_t)h * vd + cc] : (cc == vd ? 1.f : 0.f);
+            }
         }
         __syncthreads();
-        if (tid == 0) {                                    // the running maximum is a chain through the chunk
+        if (pre && t0 + ML_CHUNK < n_tok) load_chunk(t0 + ML_CHUNK);
+        if (tid == 0) {                                    // the running maximum is a chain through the chunk: an add and a max a token
+            sM[0] = m;
             for (int tt = 0; tt < nt; ++tt) {
-                const float m_new = fmaxf(sF[tt] + m, sI[tt]);
-                sA[tt] = expf(sF[tt] + m - m_new);
-                sB[tt] = expf(sI[tt] - m_new);
-                m = m_new;
-                if (blockIdx.x == 0) top[(size_t)(start + t0 + tt) * heads + h] = m_new;
+                m = fmaxf(sF[tt] + m, sI[tt]);
+                sM[tt + 1] = m;
             }
+        }
+        __syncthreads();
+        if (tid < nt) {                                    // ... the exponentials side by side
+            const float m_old = sM[tid], m_new = sM[tid + 1];
+            sA[tid] = expf(sF[tid] + m_old - m_new);
+            sB[tid] = expf(sI[tid] - m_new);
+            if (blockIdx.x == 0) top[(size_t)(start + t0 + tid) * heads + h] = m_new;
         }
         __syncthreads();
         // (threads beyond the last column walk along: the shuffles need every lane)
@@ -146,9 +217,12 @@ RV_EXPORT int rv_mlstm_scan(const float* proj, int stride, int i_col0, int f_col
     int parts = 1;
     while (parts * ns < d) parts <<= 1;                // a power of two of at most 32 lanes of one warp
     const int per_block = 128 / parts;
-    const size_t smem = sizeof(float) * (2 * (size_t)ML_CHUNK * parts * (ns + 4) + 4 * ML_CHUNK + (size_t)ML_CHUNK * per_block);
+    const size_t smem = sizeof(float) * (2 * (size_t)ML_CHUNK * parts * (ns + 4) + 5 * ML_CHUNK + 4 + (size_t)ML_CHUNK * per_block);
     if (smem > 48 * 1024) return RV_ERR_UNSUPPORTED;
-    auto kernel = ns == 32 ? mlstm_scan_kernel<32> : (ns == 16 ? mlstm_scan_kernel<16> : mlstm_scan_kernel<8>);
+    const bool pre = d <= 32 * ML_PRE_Q && per_block <= 8 * ML_PRE_V;
+    auto kernel = ns == 32 ? (pre ? mlstm_scan_kernel<32, true> : mlstm_scan_kernel<32, false>)
+                : ns == 16 ? (pre ? mlstm_scan_kernel<16, true> : mlstm_scan_kernel<16, false>)
+                           : (pre ? mlstm_scan_kernel<8, true> : mlstm_scan_kernel<8, false>);
     RV_LAUNCH_ST = rv_launch(kernel, dim3((vd + 1 + per_block - 1) / per_block, heads, n_seqs), dim3(128), smem, stream, proj, stride,
                              i_col0, f_col0, i_bias, f_bias, cu_seqlens, state_slots, state, (size_t)state_stride, raw, top, heads, d,
                              vd, parts, cap);

@@ -20,7 +20,8 @@ __device__ __forceinline__ void qp_store(void* p, int dtype, size_t i, float v) 
     else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
 }
 
-// One block per token; a warp takes one head of q, k or v at a time.
+// One block per token; a warp takes one head of q, k or v at a time.  NJ: elements of a head slot per lane (P <= 32 NJ).
+template <int NJ>
 __global__ void __launch_bounds__(QP_WARPS * 32)
 qk_unit_prepare_kernel(const float* __restrict__ proj, int row_stride, const int* __restrict__ positions,
                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int table_rows, int halves,
@@ -28,7 +29,7 @@ qk_unit_prepare_kernel(const float* __restrict__ proj, int row_stride, const int
                        float* __restrict__ gate_out, int nh, int nkv, int d, int vd, int P, int page_size, float eps, int write_kv) {
     rv_pdl_launch_dependents();
     rv_pdl_wait();
-    __shared__ float buf[QP_WARPS][QP_MAX_DIM];
+    __shared__ float buf[QP_WARPS][32 * NJ];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t row = (size_t)t * row_stride;
     int pos = positions[t];
@@ -50,10 +51,10 @@ qk_unit_prepare_kernel(const float* __restrict__ proj, int row_stride, const int
                                                          : (size_t)(nh + nkv) * d + (size_t)head * vd));
         for (int i = lane; i < n; i += 32) mine[i] = proj[src + i];
         __syncwarp();
-        float vals[QP_MAX_DIM / 32];
+        float vals[NJ];
         float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < QP_MAX_DIM / 32; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int i = lane + 32 * j;
             float v = i < n ? mine[i] : 0.f;
             if (kind != 2 && i < rot) {
@@ -87,7 +88,7 @@ qk_unit_prepare_kernel(const float* __restrict__ proj, int row_stride, const int
             dst = (((page * 2 + (kind == 2 ? 1 : 0)) * nkv + head) * page_size + off) * P;
         }
 #pragma unroll
-        for (int j = 0; j < QP_MAX_DIM / 32; ++j) {
+        for (int j = 0; j < NJ; ++j) {
             const int i = lane + 32 * j;
             if (i < P) qp_store(dst_base, out_dtype, dst + i, i < n ? vals[j] * r : 0.f);
         }
@@ -113,7 +114,9 @@ RV_EXPORT int rv_qk_unit_prepare(const float* proj, int row_stride, const int* p
     if (out_dtype & ~1) return RV_ERR_BAD_DTYPE;
     if (n_tokens == 0) return RV_OK;
     if (!cos_t || !sin_t) rot = 0;
-    RV_LAUNCH_ST = rv_launch(qk_unit_prepare_kernel, dim3(n_tokens), dim3(QP_WARPS * 32), 0, stream, proj, row_stride, positions, cos_t,
+    auto kernel = P <= 32 ? qk_unit_prepare_kernel<1> : (P <= 64 ? qk_unit_prepare_kernel<2> : (P <= 128 ? qk_unit_prepare_kernel<4>
+                                                                                                              : qk_unit_prepare_kernel<8>));
+    RV_LAUNCH_ST = rv_launch(kernel, dim3(n_tokens), dim3(QP_WARPS * 32), 0, stream, proj, row_stride, positions, cos_t,
                              sin_t, rot, table_rows, halves, slot_mapping, cache, q_out, out_dtype, gate_out, nh, nkv, d, vd, P,
                              page_size, eps, write_kv);
     return rv_launch_status();
