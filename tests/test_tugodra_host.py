@@ -349,3 +349,25 @@ def test_command_line_info_and_random_weights(tmp_path):
     assert info["architecture"] == "Tugodra" and info["config"]["layers"][4]["mixer"]["kv_from"] == 1
     cfg, w = X.read_folder(str(out))
     assert w["l0.norm1.alpha"].shape == () and P.forward(cfg, w, [1, 2, 3]).shape == (3, 131)
+
+
+def test_steps_ask_the_kernel_library_for_strict_launches(emulated):
+    """The design's specification switches programmatic dependent launch off, and the step function tells the kernel library,
+    which the engines of a process share, before every step - and switches it back on for a model that allows it."""
+    from model_tools import model_folder
+
+    class Recording(EmulatedKernels):
+        calls = []
+
+        def set_pdl(self, allowed):
+            self.calls.append(bool(allowed))
+
+    kernel_pkg.set_library(Recording())
+    folder, vocab, reqs, ref = _reference("a")
+    assert load_config(folder).to_spec().programmatic_launch is False
+    engine = trace_mod.build_engine(folder, "float32", 64, block_size=8, device="cpu")
+    engine.runner.step([StepEntry("x", reqs["r2"][:5], [4])])
+    assert Recording.calls and Recording.calls[-1] is False
+    other = trace_mod.build_engine(model_folder("tiny_llama"), "float32", 64, block_size=8, device="cpu")
+    other.runner.step([StepEntry("y", [1, 2, 3], [2])])
+    assert Recording.calls[-1] is True
