@@ -56,9 +56,10 @@ def test_dynamic_tanh_alone_and_with_the_sum(K, dtype, cols):
 def test_scaled_rows_and_squared_relu(K, dtype):
     x = rnd(7, 93, seed=8).to(dtype)
     assert K.scale_rows(x.cuda(), 13.25).dtype == torch.float32 and rel_err(K.scale_rows(x.cuda(), 13.25), x.double() * 13.25) < 1e-6
-    u, s = rnd(5, 77, seed=9, scale=2.0).float(), torch.rand(5, generator=torch.Generator().manual_seed(2))
-    assert rel_err(K.act_rows(u.cuda(), "relu2", dtype), torch.relu(u.double()) ** 2) < TOL[dtype] / 2
-    assert rel_err(K.act_rows(u.cuda(), "relu2", dtype, row_scale=s.cuda()), torch.relu(u.double()) ** 2 * s.double()[:, None]) < TOL[dtype] / 2
+    for cols in (77, 96, 2048 + 4):                           # rows off and on the four-column path
+        u, s = rnd(5, cols, seed=9, scale=2.0).float(), torch.rand(5, generator=torch.Generator().manual_seed(2))
+        assert rel_err(K.act_rows(u.cuda(), "relu2", dtype), torch.relu(u.double()) ** 2) < TOL[dtype] / 2
+        assert rel_err(K.act_rows(u.cuda(), "relu2", dtype, row_scale=s.cuda()), torch.relu(u.double()) ** 2 * s.double()[:, None]) < TOL[dtype] / 2
 
 
 # ---------------------------------------------------------------------------------------- queries and keys of the window attention
