@@ -72,6 +72,7 @@ static_assert(BN == 256 || BN == 128, "tiles of 256 or 128 columns");
 #define EPI_GATED 2
 #define EPI_GATED_GELU 4    // (launcher only) EPI_GATED with the tanh form of GELU in place of SiLU
 #define EPI_ROPE 3          // the q/k/v product: bias, rotation of q and k, k and v into the paged cache
+#define EPI_PLAIN_RELU2 6   // (launcher only) EPI_PLAIN whose results pass relu(v)^2 before they are stored
 
 struct GemmParams {
     void* out;
@@ -95,7 +96,7 @@ struct GemmParams {
     const float* cos_t;              // [table_rows, hd / 2] or nullptr (no rotation)
     const float* sin_t;
     int nh, nkv, hd, page_size, table_rows;
-    int act;                       // EPI_GATED: 0 SiLU, 1 the tanh form of GELU
+    int act;                       // EPI_GATED: 0 SiLU, 1 the tanh form of GELU; EPI_PLAIN: 0 none, 2 the square of relu
     // Grouped product (plain and gated epilogues): W holds `groups` matrices of N rows one below the other, and work
     // unit t (m_tiles of them) multiplies rows of x with matrix tile_group[t]; a negative entry marks a unit that nobody
     // uses, which every role of the kernel skips.  The rows of x are sorted by group and every group's rows padded to
@@ -131,6 +132,10 @@ __device__ __forceinline__ bool gemm_tile(const GemmParams& p, int tile, int& un
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 // the gate's activation: SiLU g sigmoid(g), or (act 1) the tanh form of GELU, which is g sigmoid(2 sqrt(2/pi) (g + 0.044715 g^3))
+__device__ __forceinline__ float plain_act(float v, int act) {
+    if (act == 2) { v = fmaxf(v, 0.f); return v * v; }
+    return v;
+}
 __device__ __forceinline__ float gate_act(float g, int act) {
     return act == 1 ? g / (1.0f + expf(-1.5957691216057308f * (g + 0.044715f * g * g * g))) : silu_f(g);
 }
@@ -584,7 +589,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 for (int j = 0; j < 4; ++j) {
                                     const int e = v * 8 + 2 * j;
                                     const float2 rf = __bfloat1622float2(rh[j]);
-                                    oh[j] = __floats2bfloat162_rn(__uint_as_float(r[e]) + rf.x, __uint_as_float(r[e + 1]) + rf.y);
+                                    oh[j] = __floats2bfloat162_rn(plain_act(__uint_as_float(r[e]) + rf.x, p.act),
+                                                                  plain_act(__uint_as_float(r[e + 1]) + rf.y, p.act));
                                 }
                                 *reinterpret_cast<uint4*>(dst + v * 8) = o;
                             }
@@ -592,14 +598,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             float4* dst = reinterpret_cast<float4*>((float*)p.out + (size_t)m * ldc + coff + n);
 #pragma unroll
                             for (int v = 0; v < 8; ++v)
-                                dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                     __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                                dst[v] = make_float4(plain_act(__uint_as_float(r[4 * v]), p.act), plain_act(__uint_as_float(r[4 * v + 1]), p.act),
+                                                     plain_act(__uint_as_float(r[4 * v + 2]), p.act), plain_act(__uint_as_float(r[4 * v + 3]), p.act));
                         } else {
 #pragma unroll
                             for (int e = 0; e < 32; ++e) {
                                 if (n + e >= p.N) continue;
                                 float val = __uint_as_float(r[e]);
                                 if (p.residual) val += __bfloat162float(p.residual[(size_t)m * p.N + n + e]);
+                                val = plain_act(val, p.act);
                                 if (p.out_f32) ((float*)p.out)[(size_t)m * ldc + coff + n + e] = val;
                                 else ((__nv_bfloat16*)p.out)[(size_t)m * ldc + coff + n + e] = __float2bfloat16_rn(val);
                             }
@@ -705,7 +712,7 @@ RV_EXPORT int rv_gemm_tcgen05_bf16(const void* x, const void* w, const void* res
 // The grouped product: x [M, K], rows sorted by group, every group's rows padded to whole blocks of 128;
 // w [groups * N, K]; on the device tile_group [units] (negative: unit unused), tile_rows [units * ranks] (first row of
 // each CTA's block, negative: none), ranks = rv_gemm_tcgen05_ranks(), and tile_order [units * rv_gemm_tcgen05_column_tiles(N,
-// epilogue)] (see GemmParams); out [M, N] (gated: N / 2 columns).  epilogue 0 (plain) or 2 (gated, SiLU).
+// epilogue)] (see GemmParams); out [M, N] (gated: N / 2 columns).  epilogue 0 (plain), 2 (gated, SiLU) or 6 (plain, results squared relu).
 RV_EXPORT int rv_gemm_tcgen05_column_tiles(int N, int epilogue) {
     return epilogue == EPI_GATED ? (N / 2 + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
 }
@@ -716,6 +723,8 @@ static int grouped_launch(const void* x, const void* w, const int* tile_group, c
                           void* out, int out_f32, int M, int N, int K, int groups, int units, int epilogue, int x_cols, int a_group_k,
                           int c_group, int ldc, int* status, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0 || groups <= 0 || units <= 0 || units > 32767 || !tile_group || !tile_rows || !tile_order) return RV_ERR_BAD_SIZE;
+    const int plain_activation = epilogue == EPI_PLAIN_RELU2 ? 2 : 0;         // the plain epilogue with an activation on its results
+    if (plain_activation) epilogue = EPI_PLAIN;
     if (epilogue != EPI_PLAIN && epilogue != EPI_GATED) return RV_ERR_UNSUPPORTED;
     if (K % 8 || x_cols % 8 || a_group_k % 8) return RV_ERR_UNSUPPORTED;       // TMA rows and column origins on 16-byte boundaries
     if ((a_group_k || c_group || ldc) && epilogue != EPI_PLAIN) return RV_ERR_UNSUPPORTED;
@@ -730,7 +739,7 @@ static int grouped_launch(const void* x, const void* w, const int* tile_group, c
     if (st != RV_OK) return st;
     GemmParams p = {};
     p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.out_f32 = out_f32; p.epilogue = epilogue;
-    p.splits = 1; p.tile_group = tile_group; p.tile_rows = tile_rows; p.tile_order = tile_order;
+    p.splits = 1; p.tile_group = tile_group; p.tile_rows = tile_rows; p.tile_order = tile_order; p.act = plain_activation;
     p.a_group_k = a_group_k; p.c_group = c_group; p.ldc = ldc;
     p.m_tiles = units;
     p.n_tiles = rv_gemm_tcgen05_column_tiles(N, epilogue);

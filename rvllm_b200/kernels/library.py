@@ -1497,8 +1497,7 @@ class CudaKernels:
     def _moe_grouped(self, x, chosen, gate_up, down, weight, add, out_dtype, weights=None, gated=True):
         """`moe_experts` for many bfloat16 tokens: the (token, slot) pairs sorted by expert, every expert's rows padded to
         whole blocks of 128, two grouped tcgen05 products over the sorted rows (gate/up with the SiLU epilogue - plain experts:
-        up with a float32 result and the squared relu in a kernel of its own - then down with a float32 result), and the
-        weighted sum per token.  Everything is decided on the device; the buffers are sized for the worst case (every
+        up with the squared relu in its epilogue - then down with a float32 result), and the weighted sum per token.  Everything is decided on the device; the buffers are sized for the worst case (every
         expert's last block nearly empty)."""
         T, width = x.shape
         E, ff2, _ = gate_up.shape
@@ -1524,12 +1523,10 @@ class CudaKernels:
                                              _ptr(order_a), c_int(nt_b), _ptr(order_b), self._stream()))
         xs = torch.empty((rows, width), dtype=torch.bfloat16, device=dev)
         _check("moe_gather", moe.rv_moe_gather(_ptr(x), _ptr(src_of), _ptr(xs), c_int(rows), c_int(width * 2), self._stream()))
-        act = torch.empty((rows, ff), dtype=torch.bfloat16 if gated else torch.float32, device=dev)
+        act = torch.empty((rows, ff), dtype=torch.bfloat16, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
-            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(order_a), _ptr(act), c_int(0 if gated else 1), c_int(rows), c_int(ff2), c_int(width), c_int(E),
-            c_int(units), c_int(epi), _ptr(self._status), self._stream()))
-        if not gated:
-            act = self.act_rows(act, "relu2", torch.bfloat16)
+            _ptr(xs), _ptr(gate_up), _ptr(tile_group), _ptr(tile_rows), _ptr(order_a), _ptr(act), c_int(0), c_int(rows), c_int(ff2), c_int(width), c_int(E),
+            c_int(units), c_int(2 if gated else 6), _ptr(self._status), self._stream()))      # (6: the plain epilogue with the squared relu)
         ys = torch.empty((rows, width), dtype=torch.float32, device=dev)
         _check("gemm_tcgen05_grouped", lib.rv_gemm_tcgen05_grouped(
             _ptr(act), _ptr(down), _ptr(tile_group), _ptr(tile_rows), _ptr(order_b), _ptr(ys), c_int(1), c_int(rows), c_int(width), c_int(ff), c_int(E),
